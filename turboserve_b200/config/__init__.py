@@ -11,6 +11,7 @@ from .engine_config import (
 )
 from .model_spec import LayerRun, LayerSpec, ModelSpec, PartSpec, TensorNames
 from .baporax import BaporaxConfig
+from .begovik import BegovikConfig
 from .filezen import FilezenConfig
 from .qwen2 import Qwen2Config, UnsupportedModelError
 from .registry import (
@@ -27,7 +28,7 @@ from .registry import (
 __all__ = [
     "EngineConfig", "FinishReason", "RequestOutput", "RequestTiming", "SamplingParams",
     "SchedulerConfig", "resolve_dtype", "LayerRun", "LayerSpec", "ModelSpec", "PartSpec",
-    "TensorNames", "BaporaxConfig", "FilezenConfig", "Qwen2Config", "UnsupportedModelError", "UnknownArchitectureError",
+    "TensorNames", "BaporaxConfig", "BegovikConfig", "FilezenConfig", "Qwen2Config", "UnsupportedModelError", "UnknownArchitectureError",
     "config_from_dict", "config_from_dir", "lookup", "read_config_json",
     "register_architecture", "registered_architectures", "unregister_architecture",
 ]

@@ -50,6 +50,8 @@ def _ensure_builtin() -> None:
         from ..models import baporax  # noqa: F401
     if "Filezen" not in _REGISTRY:
         from ..models import filezen  # noqa: F401
+    if "Begovik" not in _REGISTRY:
+        from ..models import begovik  # noqa: F401
 
 
 def architecture_of(data: Mapping[str, Any]) -> str:

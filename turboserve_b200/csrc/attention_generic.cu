@@ -30,14 +30,14 @@ paged_attention_generic_kernel(const T* __restrict__ q, long long q_stride, T* _
                                const T* __restrict__ v_pages, const int* __restrict__ block_table,
                                int table_stride, const int* __restrict__ seq_of_token,
                                const int* __restrict__ positions, int page_size, int num_heads,
-                               int num_kv_heads, int head_dim, int window, float scale,
-                               int* __restrict__ status) {
+                               int num_kv_heads, int head_dim, int v_dim, int window, float scale,
+                               float softcap, int sink, int* __restrict__ status) {
   pdl_wait();
   pdl_trigger();
   extern __shared__ float smem[];
   float* q_s = smem;                               // [head_dim]
-  float* part_acc = smem + head_dim;               // [GENERIC_STREAMS][head_dim]
-  float* part_ml = part_acc + GENERIC_STREAMS * head_dim;  // [GENERIC_STREAMS][2]
+  float* part_acc = smem + head_dim;               // [GENERIC_STREAMS][v_dim]
+  float* part_ml = part_acc + GENERIC_STREAMS * v_dim;  // [GENERIC_STREAMS][2]
 
   const int t = blockIdx.x, head = blockIdx.y;
   const int seq = seq_of_token[t];
@@ -64,14 +64,15 @@ paged_attention_generic_kernel(const T* __restrict__ q, long long q_stride, T* _
       const int key = lo + tile * 32 + lane;
       const bool valid = key <= pos;
       float s = -INFINITY;
-      size_t row = 0;
+      size_t row = 0;  // of the key's value
       if (valid) {
         const int page = table[key / page_size];
         if (page < 0) {
           if (status) atomicOr(status, 4);
         } else {
-          row = (((size_t)page * page_size + key % page_size) * num_kv_heads + kv_head) * head_dim;
-          const T* k_row = k_pages + row;
+          const size_t place = ((size_t)page * page_size + key % page_size) * num_kv_heads + kv_head;
+          row = place * v_dim;
+          const T* k_row = k_pages + place * head_dim;
           float dot = 0.0f;
           if (wide) {  // the same products in the same order, four to a load
             const float4* k4 = reinterpret_cast<const float4*>(k_row);
@@ -86,6 +87,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, long long q_stride, T* _
             for (int i = 0; i < head_dim; ++i) dot = fmaf(q_s[i], to_float(k_row[i]), dot);
           }
           s = dot * scale;
+          if (softcap > 0.0f) s = softcap * tanhf(s / softcap);
         }
       }
       const float tile_max = warp_max(s);
@@ -106,14 +108,14 @@ paged_attention_generic_kernel(const T* __restrict__ q, long long q_stride, T* _
 #pragma unroll
         for (int i = 0; i < MAX_DIMS_PER_LANE; ++i) {
           const int dim = lane + 32 * i;
-          if (dim < head_dim) acc[i] = fmaf(pj, to_float(v_row[dim]), acc[i]);
+          if (dim < v_dim) acc[i] = fmaf(pj, to_float(v_row[dim]), acc[i]);
         }
       }
     }
 #pragma unroll
     for (int i = 0; i < MAX_DIMS_PER_LANE; ++i) {
       const int dim = lane + 32 * i;
-      if (dim < head_dim) part_acc[stream * head_dim + dim] = acc[i];
+      if (dim < v_dim) part_acc[stream * v_dim + dim] = acc[i];
     }
     if (lane == 0) {
       part_ml[stream * 2] = m;
@@ -126,19 +128,57 @@ paged_attention_generic_kernel(const T* __restrict__ q, long long q_stride, T* _
     for (int w = 0; w < GENERIC_STREAMS; ++w) m_all = fmaxf(m_all, part_ml[w * 2]);
     float weight[GENERIC_STREAMS];
     float l_all = 0.0f;
+    if (sink) {  // a key whose score is 0 and whose value is nothing: it only adds to the denominator
+      m_all = fmaxf(m_all, 0.0f);
+      l_all = expf(-m_all);
+    }
     for (int w = 0; w < GENERIC_STREAMS; ++w) {
       const float mw = part_ml[w * 2];
       weight[w] = mw == -INFINITY ? 0.0f : expf(mw - m_all);
       l_all += part_ml[w * 2 + 1] * weight[w];
     }
     const float inv = l_all > 0.0f ? 1.0f / l_all : 0.0f;
-    T* o_row = out + (size_t)t * out_stride + (size_t)head * head_dim;
-    for (int dim = lane; dim < head_dim; dim += 32) {
+    T* o_row = out + (size_t)t * out_stride + (size_t)head * v_dim;
+    for (int dim = lane; dim < v_dim; dim += 32) {
       float v = 0.0f;
-      for (int w = 0; w < GENERIC_STREAMS; ++w) v += part_acc[w * head_dim + dim] * weight[w];
+      for (int w = 0; w < GENERIC_STREAMS; ++w) v += part_acc[w * v_dim + dim] * weight[w];
       o_row[dim] = from_float<T>(v * inv);
     }
   }
+}
+
+// The kernel with every option: value rows of their own width (v_dim), scores capped as
+// softcap * tanh(score / softcap) (softcap 0: as they are), and a sink (sink != 0: the softmax's
+// denominator is one larger, as if one more key scored 0 and had no value).
+TS_EXPORT int ts_paged_attention_capped(int dtype, const void* q, long long q_stride, void* out,
+                                        long long out_stride, const void* k_pages,
+                                        const void* v_pages, const int* block_table,
+                                        int table_stride, const int* seq_of_token,
+                                        const int* positions, int num_tokens, int page_size,
+                                        int num_heads, int num_kv_heads, int head_dim, int v_dim, int window,
+                                        float scale, float softcap, int sink, int* status, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (head_dim < 1 || head_dim > 32 * MAX_DIMS_PER_LANE || v_dim < 1 || v_dim > 32 * MAX_DIMS_PER_LANE) return TS_ERR_SIZE;
+  if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads) return TS_ERR_SIZE;
+  if (num_heads > 65535 || page_size < 1 || window < 0 || softcap < 0.0f) return TS_ERR_ARGUMENT;
+  dim3 grid(num_tokens, num_heads);
+  const size_t smem = ((size_t)head_dim + (size_t)v_dim * GENERIC_STREAMS + 2 * GENERIC_STREAMS) * sizeof(float);
+  // few blocks (a decode step): a warp per stream; many: four warps, four streams each
+  const int threads = (long long)num_tokens * num_heads <= 2048 ? GENERIC_STREAMS * 32 : 4 * 32;
+  if (dtype == TS_F32)
+    ts_launch(paged_attention_generic_kernel<float>, dim3(grid), dim3(threads), smem, stream, 
+        (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pages,
+        (const float*)v_pages, block_table, table_stride, seq_of_token, positions, page_size,
+        num_heads, num_kv_heads, head_dim, v_dim, window, scale, softcap, sink, status);
+  else if (dtype == TS_BF16)
+    ts_launch(paged_attention_generic_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), smem, stream, 
+        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
+        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, table_stride,
+        seq_of_token, positions, page_size, num_heads, num_kv_heads, head_dim, v_dim, window, scale,
+        softcap, sink, status);
+  else
+    return TS_ERR_DTYPE;
+  return ts_launch_status();
 }
 
 TS_EXPORT int ts_paged_attention_generic(int dtype, const void* q, long long q_stride, void* out,
@@ -148,26 +188,7 @@ TS_EXPORT int ts_paged_attention_generic(int dtype, const void* q, long long q_s
                                          const int* positions, int num_tokens, int page_size,
                                          int num_heads, int num_kv_heads, int head_dim, int window,
                                          float scale, int* status, cudaStream_t stream) {
-  if (num_tokens <= 0) return 0;
-  if (head_dim < 1 || head_dim > 32 * MAX_DIMS_PER_LANE) return TS_ERR_SIZE;
-  if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads) return TS_ERR_SIZE;
-  if (num_heads > 65535 || page_size < 1 || window < 0) return TS_ERR_ARGUMENT;
-  dim3 grid(num_tokens, num_heads);
-  const size_t smem = ((size_t)head_dim * (1 + GENERIC_STREAMS) + 2 * GENERIC_STREAMS) * sizeof(float);
-  // few blocks (a decode step): a warp per stream; many: four warps, four streams each
-  const int threads = (long long)num_tokens * num_heads <= 2048 ? GENERIC_STREAMS * 32 : 4 * 32;
-  if (dtype == TS_F32)
-    ts_launch(paged_attention_generic_kernel<float>, dim3(grid), dim3(threads), smem, stream, 
-        (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pages,
-        (const float*)v_pages, block_table, table_stride, seq_of_token, positions, page_size,
-        num_heads, num_kv_heads, head_dim, window, scale, status);
-  else if (dtype == TS_BF16)
-    ts_launch(paged_attention_generic_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), smem, stream, 
-        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
-        (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, table_stride,
-        seq_of_token, positions, page_size, num_heads, num_kv_heads, head_dim, window, scale,
-        status);
-  else
-    return TS_ERR_DTYPE;
-  return ts_launch_status();
+  return ts_paged_attention_capped(dtype, q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride,
+                                   seq_of_token, positions, num_tokens, page_size, num_heads, num_kv_heads, head_dim,
+                                   head_dim, window, scale, 0.0f, 0, status, stream);
 }

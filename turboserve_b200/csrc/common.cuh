@@ -77,6 +77,18 @@ __device__ __forceinline__ float activation(float x, int act) {
   return 0.5f * x * (1.0f + tanhf(inner));
 }
 
+// What a gated feed-forward keeps of a gate value g and an up value u.  Codes 0 to 2: act(g) * u with the
+// activation above.  Code 3, the clamped form: g' = min(g, limit), u' = clamp(u, -limit, limit),
+// g' * sigmoid(alpha * g') * (u' + 1); `limit` and `alpha` are the part's constants.
+template <bool FAST = false>
+__device__ __forceinline__ float gated_value(float g, float u, int act, float limit, float alpha) {
+  if (act < 3) return activation<FAST>(g, act) * u;
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  const float s = FAST ? __fdividef(1.0f, 1.0f + __expf(-alpha * g)) : 1.0f / (1.0f + expf(-alpha * g));
+  return g * s * (u + 1.0f);
+}
+
 static inline int ts_launch_status() { return (int)cudaGetLastError(); }
 
 // Programmatic dependent launch.  Every kernel of the package is launched with the attribute

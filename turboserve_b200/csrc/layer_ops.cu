@@ -217,14 +217,14 @@ TS_EXPORT int ts_add_rmsnorm(int dtype, float* residual, const void* delta, cons
 
 // ---------------------------------------------------------------------------------------
 // Gated activation: out[t, i] = act(gate_up[t, i]) * gate_up[t, inter + i].
-//   act: 0 silu, 1 gelu (erf), 2 gelu (tanh approximation)
+//   act: 0 silu, 1 gelu (erf), 2 gelu (tanh approximation); 3: the clamped form (gated_value in common.cuh)
 // ---------------------------------------------------------------------------------------
 // VEC elements per thread: 16 bytes when the row width allows it (8 bfloat16 or 4 float), else 1.
 // block == 0: a row is [gate(inter) | up(inter)].  block > 0 (a multiple of the vector width that
 // divides inter): gate and up alternate in runs of `block` features, [g 0..b-1 | u 0..b-1 | g b.. ].
 template <typename T, int VEC>
 __global__ void act_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter,
-                               int act, int block) {
+                               int act, int block, float limit, float alpha) {
   pdl_wait();
   pdl_trigger<1>();
   const size_t t = blockIdx.x;
@@ -234,7 +234,7 @@ __global__ void act_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ ou
   const int gate_at = block > 0 ? (i / block) * 2 * block + i % block : i;
   const int up_at = block > 0 ? gate_at + block : inter + i;
   if constexpr (VEC == 1) {
-    out[t * inter + i] = from_float<T>(activation<sizeof(T) == 2>(to_float(row[gate_at]), act) * to_float(row[up_at]));
+    out[t * inter + i] = from_float<T>(gated_value<sizeof(T) == 2>(to_float(row[gate_at]), to_float(row[up_at]), act, limit, alpha));
   } else {
 #pragma unroll
     for (int part = 0; part < VEC / 4; ++part) {  // a 16-byte load is two Vec4 halves for bfloat16
@@ -242,7 +242,7 @@ __global__ void act_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ ou
       Vec4<T>::load(row + gate_at + 4 * part, g);
       Vec4<T>::load(row + up_at + 4 * part, u);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) g[e] = activation<sizeof(T) == 2>(g[e], act) * u[e];
+      for (int e = 0; e < 4; ++e) g[e] = gated_value<sizeof(T) == 2>(g[e], u[e], act, limit, alpha);
       Vec4<T>::store(out + t * inter + i + 4 * part, g);
     }
   }
@@ -252,7 +252,7 @@ __global__ void act_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ ou
 // of them per operand in flight per thread.
 __global__ void __launch_bounds__(256)
 act_mul_bf16_wide_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter,
-                         int act, int block) {
+                         int act, int block, float limit, float alpha) {
   pdl_wait();
   pdl_trigger<1>();
   const size_t t = blockIdx.x;
@@ -279,8 +279,8 @@ act_mul_bf16_wide_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat1
     for (int e = 0; e < 4; ++e) {
       const __nv_bfloat162 gp = *reinterpret_cast<const __nv_bfloat162*>(&gw[e]);
       const __nv_bfloat162 up = *reinterpret_cast<const __nv_bfloat162*>(&uw[e]);
-      const __nv_bfloat162 o = __floats2bfloat162_rn(activation<true>(__low2float(gp), act) * __low2float(up),
-                                                     activation<true>(__high2float(gp), act) * __high2float(up));
+      const __nv_bfloat162 o = __floats2bfloat162_rn(gated_value<true>(__low2float(gp), __low2float(up), act, limit, alpha),
+                                                     gated_value<true>(__high2float(gp), __high2float(up), act, limit, alpha));
       ow[e] = *reinterpret_cast<const unsigned*>(&o);
     }
     *reinterpret_cast<uint4*>(out + t * inter + at[v]) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
@@ -288,7 +288,8 @@ act_mul_bf16_wide_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat1
 }
 
 template <typename T>
-static int launch_act_mul(const T* gate_up, T* out, int num_tokens, int inter, int act, int block, cudaStream_t stream) {
+static int launch_act_mul(const T* gate_up, T* out, int num_tokens, int inter, int act, int block, float limit, float alpha,
+                          cudaStream_t stream) {
   constexpr int WIDE = 16 / sizeof(T);
   const bool aligned = !(((uintptr_t)gate_up | (uintptr_t)out) & 15);
   const int vec = (aligned && inter % WIDE == 0) ? WIDE : ((aligned && inter % 4 == 0) ? 4 : 1);
@@ -297,7 +298,7 @@ static int launch_act_mul(const T* gate_up, T* out, int num_tokens, int inter, i
     if (vec == WIDE && num_tokens >= 32) {  // many rows: the wide kernel (few rows are latency-bound either way)
       const int blocks_y = (inter + 256 * 16 - 1) / (256 * 16);
       if (blocks_y > 65535) return TS_ERR_SIZE;
-      ts_launch(act_mul_bf16_wide_kernel, dim3(num_tokens, blocks_y), dim3(256), 0, stream, gate_up, out, inter, act, block);
+      ts_launch(act_mul_bf16_wide_kernel, dim3(num_tokens, blocks_y), dim3(256), 0, stream, gate_up, out, inter, act, block, limit, alpha);
       return ts_launch_status();
     }
   }
@@ -305,21 +306,21 @@ static int launch_act_mul(const T* gate_up, T* out, int num_tokens, int inter, i
   if ((inter + per_block - 1) / per_block > 65535) return TS_ERR_SIZE;
   dim3 grid(num_tokens, (inter + per_block - 1) / per_block);
   if (vec == WIDE)
-    ts_launch(act_mul_kernel<T, WIDE>, dim3(grid), dim3(256), 0, stream, gate_up, out, inter, act, block);
+    ts_launch(act_mul_kernel<T, WIDE>, dim3(grid), dim3(256), 0, stream, gate_up, out, inter, act, block, limit, alpha);
   else if (vec == 4)
-    ts_launch(act_mul_kernel<T, 4>, dim3(grid), dim3(256), 0, stream, gate_up, out, inter, act, block);
+    ts_launch(act_mul_kernel<T, 4>, dim3(grid), dim3(256), 0, stream, gate_up, out, inter, act, block, limit, alpha);
   else
-    ts_launch(act_mul_kernel<T, 1>, dim3(grid), dim3(256), 0, stream, gate_up, out, inter, act, block);
+    ts_launch(act_mul_kernel<T, 1>, dim3(grid), dim3(256), 0, stream, gate_up, out, inter, act, block, limit, alpha);
   return ts_launch_status();
 }
 
 TS_EXPORT int ts_act_mul(int dtype, const void* gate_up, void* out, int num_tokens, int inter,
-                         int act, int block, cudaStream_t stream) {
+                         int act, int block, float limit, float alpha, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
-  if (act < 0 || act > 2) return TS_ERR_ARGUMENT;
-  if (dtype == TS_F32) return launch_act_mul<float>((const float*)gate_up, (float*)out, num_tokens, inter, act, block, stream);
+  if (act < 0 || act > 3) return TS_ERR_ARGUMENT;
+  if (dtype == TS_F32) return launch_act_mul<float>((const float*)gate_up, (float*)out, num_tokens, inter, act, block, limit, alpha, stream);
   if (dtype == TS_BF16)
-    return launch_act_mul<__nv_bfloat16>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, num_tokens, inter, act, block, stream);
+    return launch_act_mul<__nv_bfloat16>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, num_tokens, inter, act, block, limit, alpha, stream);
   return TS_ERR_DTYPE;
 }
 
@@ -566,6 +567,109 @@ TS_EXPORT int ts_rope_cache_write(int dtype, void* qkv, long long row_stride, co
         (__nv_bfloat16*)qkv, row_stride, bias, positions, seq_of_token, block_table, table_stride,
         (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, page_size, num_heads, num_kv_heads,
         head_dim, inv_freq, rotary_dim, factor, write_kv, status);
+  else
+    return TS_ERR_DTYPE;
+  return ts_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
+// Norm per head + rotation + KV append, for key rows and value rows of widths of their own.
+//   qkv: [tokens, row_stride]: num_heads query heads and then num_kv_heads key heads of `dim` elements, then
+//        num_kv_heads value heads of `vdim` elements.
+//   With a gain (q_gain for queries, k_gain for keys; `dim` floats shared by all heads) a head is divided by its
+//   root mean square (eps inside the root) and multiplied by the gain, in fp32, before the rotation.  The
+//   rotation turns pair i < rotary_dim / 2 by float(pos) * inv_freq[i]: the pair is elements (2i, 2i + 1) when
+//   `interleaved`, else (i, i + rotary_dim / 2).  Queries are written back in place, keys to k_pages
+//   [pages, page_size, kv_heads, dim], values (unchanged) to v_pages [pages, page_size, kv_heads, vdim].
+//   One warp per (token, projected head); the head passes through shared memory, so any pairing and any width
+//   up to HEAD_PREPARE_MAX elements is taken.  Status bits as in the kernel above.
+// ---------------------------------------------------------------------------------------
+#define HEAD_PREPARE_MAX 256
+#define HEAD_PREPARE_WARPS 8
+template <typename T>
+__global__ void __launch_bounds__(32 * HEAD_PREPARE_WARPS)
+head_norm_rope_write_kernel(T* __restrict__ qkv, long long row_stride, const float* __restrict__ q_gain,
+                            const float* __restrict__ k_gain, float eps, const int* __restrict__ positions,
+                            const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int table_stride,
+                            T* __restrict__ k_pages, T* __restrict__ v_pages, int page_size, int num_heads,
+                            int num_kv_heads, int dim, int vdim, const float* __restrict__ inv_freq, int rotary_dim,
+                            int interleaved, int write_kv, int* __restrict__ status) {
+  __shared__ float heads_s[HEAD_PREPARE_WARPS][HEAD_PREPARE_MAX];
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.y * HEAD_PREPARE_WARPS + warp;
+  const int seq = head < num_heads + 2 * num_kv_heads ? seq_of_token[t] : -1;
+  pdl_wait();
+  pdl_trigger<64>();
+  if (seq < 0) return;
+  const int pos = positions[t];
+  const bool is_q = head < num_heads, is_k = !is_q && head < num_heads + num_kv_heads;
+  const int width = (is_q || is_k) ? dim : vdim;
+  T* x = qkv + (size_t)t * row_stride +
+         (is_q || is_k ? (size_t)head * dim : (size_t)(num_heads + num_kv_heads) * dim + (size_t)(head - num_heads - num_kv_heads) * vdim);
+  T* dst = x;
+  if (!is_q) {
+    if (!write_kv) return;
+    const int page = block_table[(size_t)seq * table_stride + pos / page_size];
+    if (page < 0) {
+      if (lane == 0 && status) atomicOr(status, 2);
+      return;
+    }
+    const size_t place = (size_t)page * page_size + pos % page_size;
+    dst = is_k ? k_pages + (place * num_kv_heads + (head - num_heads)) * dim
+               : v_pages + (place * num_kv_heads + (head - num_heads - num_kv_heads)) * vdim;
+  }
+  if (!is_q && !is_k) {
+    for (int i = lane; i < width; i += 32) dst[i] = x[i];
+    return;
+  }
+  float* h = heads_s[warp];
+  const float* gain = is_q ? q_gain : k_gain;
+  float sum_sq = 0.0f;
+  for (int i = lane; i < dim; i += 32) {
+    const float v = to_float(x[i]);
+    h[i] = v;
+    sum_sq = fmaf(v, v, sum_sq);
+  }
+  if (gain) {
+    sum_sq = warp_sum(sum_sq);
+    const float inv = 1.0f / sqrtf(sum_sq / (float)dim + eps);
+    for (int i = lane; i < dim; i += 32) h[i] = h[i] * inv * gain[i];
+  }
+  __syncwarp();
+  const int half = rotary_dim / 2;
+  for (int i = lane; i < half; i += 32) {
+    const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+    float s, c, o1, o2;
+    sincosf((float)pos * inv_freq[i], &s, &c);
+    rope_rotate(h[a], h[b], c, s, o1, o2);
+    dst[a] = from_float<T>(o1);
+    dst[b] = from_float<T>(o2);
+  }
+  for (int i = rotary_dim + lane; i < dim; i += 32) dst[i] = from_float<T>(h[i]);
+}
+
+TS_EXPORT int ts_head_norm_rope_write(int dtype, void* qkv, long long row_stride, const float* q_gain, const float* k_gain,
+                                      float eps, const int* positions, const int* seq_of_token, const int* block_table,
+                                      int table_stride, void* k_pages, void* v_pages, int page_size, int num_tokens,
+                                      int num_heads, int num_kv_heads, int dim, int vdim, const float* inv_freq,
+                                      int rotary_dim, int interleaved, int write_kv, int* status, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (dim < 1 || dim > HEAD_PREPARE_MAX || vdim < 1) return TS_ERR_SIZE;
+  if (rotary_dim < 0 || rotary_dim > dim || (rotary_dim & 1)) return TS_ERR_SIZE;
+  if (rotary_dim > 0 && inv_freq == nullptr) return TS_ERR_ARGUMENT;
+  if (page_size < 1 || (write_kv && (!k_pages || !v_pages || !block_table))) return TS_ERR_ARGUMENT;
+  const int heads = num_heads + 2 * num_kv_heads;
+  if (heads <= 0 || heads > 65535 * HEAD_PREPARE_WARPS) return TS_ERR_SIZE;
+  dim3 grid(num_tokens, (heads + HEAD_PREPARE_WARPS - 1) / HEAD_PREPARE_WARPS);
+  if (dtype == TS_F32)
+    ts_launch(head_norm_rope_write_kernel<float>, grid, dim3(32 * HEAD_PREPARE_WARPS), 0, stream, (float*)qkv, row_stride,
+              q_gain, k_gain, eps, positions, seq_of_token, block_table, table_stride, (float*)k_pages, (float*)v_pages,
+              page_size, num_heads, num_kv_heads, dim, vdim, inv_freq, rotary_dim, interleaved, write_kv, status);
+  else if (dtype == TS_BF16)
+    ts_launch(head_norm_rope_write_kernel<__nv_bfloat16>, grid, dim3(32 * HEAD_PREPARE_WARPS), 0, stream,
+              (__nv_bfloat16*)qkv, row_stride, q_gain, k_gain, eps, positions, seq_of_token, block_table, table_stride,
+              (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, page_size, num_heads, num_kv_heads, dim, vdim, inv_freq,
+              rotary_dim, interleaved, write_kv, status);
   else
     return TS_ERR_DTYPE;
   return ts_launch_status();

@@ -349,3 +349,162 @@ TS_EXPORT int ts_gated_group_norm(int dtype, const float* y, const void* z, long
     return TS_ERR_DTYPE;
   return ts_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------
+// selective_scan: the state-space recurrence with a state per channel and a decay per channel and state index.
+//
+// Per channel c (of `inner`), state index n (of N) and position t, all in fp32:
+//
+//   dt_t[c]  = softplus(dt_raw_t[c] + dt_bias[c])
+//   S_t[c,n] = exp(dt_t[c] * A[c,n]) * S_{t-1}[c,n] + dt_t[c] * x_t[c] * B_t[n],        A = -exp(A_log)
+//   y_t[c]   = sum_n S_t[c,n] * C_t[n] + D[c] * x_t[c]
+//   out_t[c] = y_t[c] * silu(z_t[c])                                  (rounded once)
+//
+// x is the convolved and activated input, B_t and C_t columns of the low-rank projection of x, dt_raw the fp32
+// product of its first columns with the step-size matrix, z the gate half of the input projection.  The state of a
+// request lives in its slot ([slots][inner][N], fp32), is read once before the step's first position of the
+// request and written once after its last.  A block owns one request and SEL_THREADS / L channels; L lanes share a
+// channel, lane l holding states l, l + L, ... in registers (at most SEL_PER_LANE of them), and add their parts of
+// y by shuffles in a fixed order.  Positions come SEL_BATCH at a time through shared memory.  One token per request
+// and long portions run the same code, so an output is the same bits however a request is cut into steps.
+// ---------------------------------------------------------------------------------------
+#define SEL_THREADS 128
+#define SEL_BATCH 8
+#define SEL_PER_LANE 16
+
+template <typename T, int NPL>  // NPL: states a lane (1, 2, 4, 8 or 16)
+__global__ void __launch_bounds__(SEL_THREADS)
+selective_scan_kernel(const T* __restrict__ x, long long x_stride, const float* __restrict__ dt_raw,
+                      const float* __restrict__ dt_bias, const T* __restrict__ bc, long long bc_stride, int b_first,
+                      int c_first, const float* __restrict__ a_log, const float* __restrict__ d_skip,
+                      const T* __restrict__ z, long long z_stride, float* __restrict__ state, T* __restrict__ out,
+                      long long out_stride, const int* __restrict__ query_start, const int* __restrict__ slots, int inner,
+                      int n_state, int lanes) {
+  extern __shared__ __align__(16) float sel_smem[];
+  const int channels = SEL_THREADS / lanes;              // channels a block
+  const int npad = lanes * NPL;                          // states, padded
+  float* x_s = sel_smem;                                 // [SEL_BATCH][channels]
+  float* dt_s = x_s + SEL_BATCH * channels;              // [SEL_BATCH][channels]
+  float* z_s = dt_s + SEL_BATCH * channels;              // [SEL_BATCH][channels]
+  float* b_s = z_s + SEL_BATCH * channels;               // [SEL_BATCH][npad]
+  float* c_s = b_s + SEL_BATCH * npad;                   // [SEL_BATCH][npad]
+  const int seq = blockIdx.x, tid = threadIdx.x;
+  const int dl = tid % lanes, cl = tid / lanes, ch = blockIdx.y * channels + cl;
+  const bool live = ch < inner;
+  float a[NPL], s[NPL];
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) {
+    const int n = dl + i * lanes;
+    a[i] = (live && n < n_state) ? -expf(a_log[(size_t)ch * n_state + n]) : 0.0f;
+  }
+  const float bias = live ? dt_bias[ch] : 0.0f, skip = live ? d_skip[ch] : 0.0f;
+  pdl_wait();
+  pdl_trigger();
+  const int first = query_start[seq], last = query_start[seq + 1];
+  if (last <= first) return;
+  float* s_ptr = state + ((size_t)slots[seq] * inner + (live ? ch : 0)) * n_state;
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) {
+    const int n = dl + i * lanes;
+    s[i] = (live && n < n_state) ? s_ptr[n] : 0.0f;
+  }
+  for (int t0 = first; t0 < last; t0 += SEL_BATCH) {
+    const int count = min(SEL_BATCH, last - t0);
+    __syncthreads();  // everyone is done with the batch before
+    for (int idx = tid; idx < count * channels; idx += SEL_THREADS) {
+      const int p = idx / channels, c = blockIdx.y * channels + idx % channels;
+      float xv = 0.0f, dv = 0.0f, zv = 0.0f;
+      if (c < inner) {
+        xv = to_float(x[(size_t)(t0 + p) * x_stride + c]);
+        const float raw = dt_raw[(size_t)(t0 + p) * inner + c] + dt_bias[c];
+        dv = raw > 20.0f ? raw : log1pf(expf(raw));
+        zv = to_float(z[(size_t)(t0 + p) * z_stride + c]);
+      }
+      x_s[idx] = xv;
+      dt_s[idx] = dv;
+      z_s[idx] = zv;
+    }
+    for (int idx = tid; idx < count * npad; idx += SEL_THREADS) {
+      const int p = idx / npad, n = idx % npad;
+      const T* row = bc + (size_t)(t0 + p) * bc_stride;
+      b_s[idx] = n < n_state ? to_float(row[b_first + n]) : 0.0f;
+      c_s[idx] = n < n_state ? to_float(row[c_first + n]) : 0.0f;
+    }
+    __syncthreads();
+    for (int p = 0; p < count; ++p) {
+      const float xv = x_s[p * channels + cl], dt = dt_s[p * channels + cl];
+      const float dx = dt * xv;
+      const float* bp = b_s + p * npad + dl;
+      const float* cp = c_s + p * npad + dl;
+      float y = 0.0f;
+#pragma unroll
+      for (int i = 0; i < NPL; ++i) {
+        s[i] = fmaf(expf(dt * a[i]), s[i], dx * bp[i * lanes]);
+        y = fmaf(s[i], cp[i * lanes], y);
+      }
+      for (int offset = lanes >> 1; offset > 0; offset >>= 1) y += __shfl_xor_sync(0xffffffffu, y, offset);
+      if (dl == 0 && live) {
+        const float zv = z_s[p * channels + cl];
+        out[(size_t)(t0 + p) * out_stride + ch] = from_float<T>(fmaf(skip, xv, y) * (zv / (1.0f + expf(-zv))));
+      }
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int n = dl + i * lanes;
+      if (n < n_state) s_ptr[n] = s[i];
+    }
+  }
+  (void)bias;
+}
+
+template <typename T>
+static int launch_selective_scan(const T* x, long long x_stride, const float* dt_raw, const float* dt_bias, const T* bc,
+                                 long long bc_stride, int b_first, int c_first, const float* a_log, const float* d_skip,
+                                 const T* z, long long z_stride, float* state, T* out, long long out_stride,
+                                 const int* query_start, const int* slots, int num_seqs, int inner, int n_state,
+                                 cudaStream_t stream) {
+  // lanes a channel: the fewest (a power of two up to 32) that leave a lane at most SEL_PER_LANE states; a lane's
+  // count is rounded up to a power of two
+  int lanes = 1;
+  while (lanes < 32 && (n_state + lanes - 1) / lanes > SEL_PER_LANE) lanes <<= 1;
+  int npl = 1;
+  while (npl * lanes < n_state) npl <<= 1;
+  if (npl > SEL_PER_LANE) return TS_ERR_SIZE;
+  const int channels = SEL_THREADS / lanes;
+  dim3 grid(num_seqs, (inner + channels - 1) / channels);
+  if (grid.y > 65535) return TS_ERR_SIZE;
+  const size_t smem = (size_t)SEL_BATCH * (3 * channels + 2 * lanes * npl) * sizeof(float);
+#define SEL_LAUNCH(N)                                                                                                    \
+  ts_launch(selective_scan_kernel<T, N>, grid, dim3(SEL_THREADS), smem, stream, x, x_stride, dt_raw, dt_bias, bc, bc_stride, \
+            b_first, c_first, a_log, d_skip, z, z_stride, state, out, out_stride, query_start, slots, inner, n_state, lanes)
+  switch (npl) {
+    case 1: SEL_LAUNCH(1); break;
+    case 2: SEL_LAUNCH(2); break;
+    case 4: SEL_LAUNCH(4); break;
+    case 8: SEL_LAUNCH(8); break;
+    default: SEL_LAUNCH(16); break;
+  }
+#undef SEL_LAUNCH
+  return ts_launch_status();
+}
+
+TS_EXPORT int ts_selective_scan(int dtype, const void* x, long long x_stride, const float* dt_raw, const float* dt_bias,
+                                const void* bc, long long bc_stride, int b_first, int c_first, const float* a_log,
+                                const float* d_skip, const void* z, long long z_stride, float* state, void* out,
+                                long long out_stride, const int* query_start, const int* slots, int num_seqs, int inner,
+                                int n_state, cudaStream_t stream) {
+  if (num_seqs <= 0) return 0;
+  if (inner < 1 || n_state < 1 || n_state > 32 * SEL_PER_LANE) return TS_ERR_SIZE;
+  if (dtype == TS_F32)
+    return launch_selective_scan<float>((const float*)x, x_stride, dt_raw, dt_bias, (const float*)bc, bc_stride, b_first,
+                                        c_first, a_log, d_skip, (const float*)z, z_stride, state, (float*)out, out_stride,
+                                        query_start, slots, num_seqs, inner, n_state, stream);
+  if (dtype == TS_BF16)
+    return launch_selective_scan<__nv_bfloat16>((const __nv_bfloat16*)x, x_stride, dt_raw, dt_bias, (const __nv_bfloat16*)bc,
+                                                bc_stride, b_first, c_first, a_log, d_skip, (const __nv_bfloat16*)z, z_stride,
+                                                state, (__nv_bfloat16*)out, out_stride, query_start, slots, num_seqs, inner,
+                                                n_state, stream);
+  return TS_ERR_DTYPE;
+}

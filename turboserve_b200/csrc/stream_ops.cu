@@ -2,7 +2,8 @@
 // element-wise ones: a plain (ungated) activation and a scaling of rows.
 //
 //   stream_norm   x = residual + delta_a + delta_b + shift (each optional), summed in fp32 in that
-//                 order; written back to the residual (unless rows are selected); then
+//                 order (with a factor other than 1: residual + mult * (delta_a + delta_b) + shift);
+//                 written back to the residual (unless rows are selected); then
 //                 out1 = x * rsqrt(mean(x^2) + eps) * gain1 and, if asked, out2 = the same * gain2.
 //                 One launch does what a layer with two parallel branches needs between the branches
 //                 of the layer before and its own: both pending updates, the vector that a repeated
@@ -11,7 +12,7 @@
 //   norm_add      residual += mult * (update * rsqrt(mean(update^2) + eps) * gain), the norm taken on a
 //                 sublayer's OUTPUT, all in fp32; the new residual is also written in the activation
 //                 type as the next sublayer's input.  Without an update it only writes that copy.
-//   activation    out = act(in), act one of relu^2, gelu(tanh), silu, in fp32, rounded once.
+//   activation    out = act(in), act one of relu^2, gelu(tanh), silu, tanh, in fp32, rounded once.
 //   scale_rows    fp32 rows times a constant, in place (a head whose logits are scaled).
 #include "common.cuh"
 
@@ -20,7 +21,7 @@ __global__ void stream_norm_kernel(float* __restrict__ residual, const T* __rest
                                    const T* __restrict__ delta_b, const float* __restrict__ shift,
                                    const float* __restrict__ gain1, T* __restrict__ out1,
                                    const float* __restrict__ gain2, T* __restrict__ out2,
-                                   const int* __restrict__ rows, int hidden, float eps) {
+                                   const int* __restrict__ rows, int hidden, float eps, float mult) {
   extern __shared__ __align__(16) float row_cache[];
   __shared__ float scratch[33];
   const int r = blockIdx.x;
@@ -33,8 +34,14 @@ __global__ void stream_norm_kernel(float* __restrict__ residual, const T* __rest
   float sum_sq = 0.0f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float x = res[i];
-    if (da) x += to_float(da[i]);
-    if (db) x += to_float(db[i]);
+    if (mult == 1.0f) {
+      if (da) x += to_float(da[i]);
+      if (db) x += to_float(db[i]);
+    } else {
+      float u = da ? to_float(da[i]) : 0.0f;
+      if (db) u += to_float(db[i]);
+      x = fmaf(mult, u, x);
+    }
     if (shift) x += shift[i];
     row_cache[i] = x;
     if (!rows) res[i] = x;
@@ -54,7 +61,7 @@ __global__ void stream_norm_kernel(float* __restrict__ residual, const T* __rest
 
 TS_EXPORT int ts_stream_norm(int dtype, float* residual, const void* delta_a, const void* delta_b,
                              const float* shift, const float* gain1, void* out1, const float* gain2,
-                             void* out2, const int* rows, int num_rows, int hidden, float eps,
+                             void* out2, const int* rows, int num_rows, int hidden, float eps, float mult,
                              cudaStream_t stream) {
   if (num_rows <= 0) return 0;
   if (hidden < 1 || (size_t)hidden * sizeof(float) > 200 * 1024) return TS_ERR_SIZE;
@@ -66,13 +73,13 @@ TS_EXPORT int ts_stream_norm(int dtype, float* residual, const void* delta_a, co
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(stream_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ts_launch(stream_norm_kernel<float>, dim3(num_rows), dim3(threads), smem, stream, residual, (const float*)delta_a,
-              (const float*)delta_b, shift, gain1, (float*)out1, gain2, (float*)out2, rows, hidden, eps);
+              (const float*)delta_b, shift, gain1, (float*)out1, gain2, (float*)out2, rows, hidden, eps, mult);
   } else if (dtype == TS_BF16) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(stream_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ts_launch(stream_norm_kernel<__nv_bfloat16>, dim3(num_rows), dim3(threads), smem, stream, residual,
               (const __nv_bfloat16*)delta_a, (const __nv_bfloat16*)delta_b, shift, gain1, (__nv_bfloat16*)out1, gain2,
-              (__nv_bfloat16*)out2, rows, hidden, eps);
+              (__nv_bfloat16*)out2, rows, hidden, eps, mult);
   } else {
     return TS_ERR_DTYPE;
   }
@@ -137,7 +144,7 @@ TS_EXPORT int ts_norm_add(int dtype, float* residual, const void* update, const 
   return ts_launch_status();
 }
 
-// out = act(in): 0 relu^2, 1 gelu (tanh form), 2 silu.
+// out = act(in): 0 relu^2, 1 gelu (tanh form), 2 silu, 3 tanh.
 __device__ __forceinline__ float plain_activation(float x, int act) {
   if (act == 0) {
     const float r = fmaxf(x, 0.0f);
@@ -147,6 +154,7 @@ __device__ __forceinline__ float plain_activation(float x, int act) {
     const float inner = 0.79788456080286535588f * (x + 0.044715f * x * x * x);
     return 0.5f * x * (1.0f + tanhf(inner));
   }
+  if (act == 3) return tanhf(x);
   return x / (1.0f + expf(-x));
 }
 
@@ -161,7 +169,7 @@ __global__ void activation_kernel(const T* __restrict__ in, T* __restrict__ out,
 
 TS_EXPORT int ts_activation(int dtype, const void* in, void* out, long long count, int act, cudaStream_t stream) {
   if (count <= 0) return 0;
-  if (act < 0 || act > 2) return TS_ERR_ARGUMENT;
+  if (act < 0 || act > 3) return TS_ERR_ARGUMENT;
   long long blocks = (count + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (dtype == TS_F32)
@@ -186,5 +194,122 @@ TS_EXPORT int ts_scale_rows(float* data, long long count, float factor, cudaStre
   long long blocks = (count + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   ts_launch(scale_rows_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, data, count, factor);
+  return ts_launch_status();
+}
+
+
+// ---------------------------------------------------------------------------------------
+// norm_pair_mix: out = wa * (a / rms(a) * gain_a) + wb * (b / rms(b) * gain_b), each input normed over the whole
+// row on its own (eps inside the root), in fp32, rounded once.  Two mixers that read the same input side by
+// side leave their outputs this way as one update of the stream.  One block per row.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void norm_pair_mix_kernel(const T* __restrict__ a, const T* __restrict__ b, const float* __restrict__ gain_a,
+                                     const float* __restrict__ gain_b, T* __restrict__ out, int hidden, float eps,
+                                     float wa, float wb) {
+  extern __shared__ __align__(16) float row_cache[];  // [2][hidden]
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  pdl_wait();
+  pdl_trigger<1>();
+  const T* ra = a + (size_t)r * hidden;
+  const T* rb = b + (size_t)r * hidden;
+  float sa = 0.0f, sb = 0.0f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float x = to_float(ra[i]), y = to_float(rb[i]);
+    row_cache[i] = x;
+    row_cache[hidden + i] = y;
+    sa = fmaf(x, x, sa);
+    sb = fmaf(y, y, sb);
+  }
+  const float ta = block_sum(sa, scratch);
+  const float tb = block_sum(sb, scratch);
+  const float ia = wa / sqrtf(ta / (float)hidden + eps), ib = wb / sqrtf(tb / (float)hidden + eps);
+  T* o = out + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    o[i] = from_float<T>(fmaf(row_cache[i] * ia, gain_a[i], row_cache[hidden + i] * ib * gain_b[i]));
+}
+
+TS_EXPORT int ts_norm_pair_mix(int dtype, const void* a, const void* b, const float* gain_a, const float* gain_b, void* out,
+                               int num_rows, int hidden, float eps, float wa, float wb, cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  if (hidden < 1 || (size_t)hidden * 2 * sizeof(float) > 200 * 1024) return TS_ERR_SIZE;
+  int threads = (hidden + 31) / 32 * 32;
+  threads = threads < 64 ? 64 : (threads > 512 ? 512 : threads);
+  const size_t smem = (size_t)hidden * 2 * sizeof(float);
+  if (dtype == TS_F32) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(norm_pair_mix_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ts_launch(norm_pair_mix_kernel<float>, dim3(num_rows), dim3(threads), smem, stream, (const float*)a, (const float*)b,
+              gain_a, gain_b, (float*)out, hidden, eps, wa, wb);
+  } else if (dtype == TS_BF16) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(norm_pair_mix_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ts_launch(norm_pair_mix_kernel<__nv_bfloat16>, dim3(num_rows), dim3(threads), smem, stream, (const __nv_bfloat16*)a,
+              (const __nv_bfloat16*)b, gain_a, gain_b, (__nv_bfloat16*)out, hidden, eps, wa, wb);
+  } else {
+    return TS_ERR_DTYPE;
+  }
+  return ts_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
+// shift_mix: blends of every token's row with the row of the token before it in its request,
+//     out[t][s] = x[t] + (x[t - 1] - x[t]) * mu[s]          (s = 0 .. mixes - 1, mu[s] a row of floats)
+// written side by side as [tokens][mixes * hidden].  The row before a step's first token of a request is the one
+// the request kept in its state slot (`last`, [slots][hidden], in the activation type); before position 0 it is
+// zeros.  A second kernel then keeps each request's last row of this step.  fp32 arithmetic, rounded once.
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void shift_mix_kernel(const T* __restrict__ x, const float* __restrict__ mu, const T* __restrict__ last,
+                                 T* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                 const int* __restrict__ query_start, const int* __restrict__ slots, int hidden, int mixes) {
+  const int t = blockIdx.x;
+  const int seq = seq_of_token[t];
+  pdl_wait();
+  pdl_trigger<1>();
+  if (seq < 0) return;
+  const T* before = nullptr;
+  if (positions[t] > 0) before = t > query_start[seq] ? x + (size_t)(t - 1) * hidden : last + (size_t)slots[seq] * hidden;
+  const T* row = x + (size_t)t * hidden;
+  T* o = out + (size_t)t * mixes * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float now = to_float(row[i]);
+    const float step = (before ? to_float(before[i]) : 0.0f) - now;
+    for (int s = 0; s < mixes; ++s) o[(size_t)s * hidden + i] = from_float<T>(fmaf(step, mu[(size_t)s * hidden + i], now));
+  }
+}
+
+template <typename T>
+__global__ void shift_keep_kernel(const T* __restrict__ x, T* __restrict__ last, const int* __restrict__ query_start,
+                                  const int* __restrict__ slots, int hidden) {
+  const int seq = blockIdx.x;
+  pdl_wait();
+  const int first = query_start[seq], end = query_start[seq + 1];
+  if (end <= first) return;
+  const T* row = x + (size_t)(end - 1) * hidden;
+  T* to = last + (size_t)slots[seq] * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) to[i] = row[i];
+}
+
+TS_EXPORT int ts_shift_mix(int dtype, const void* x, const float* mu, void* last, void* out, const int* positions,
+                           const int* seq_of_token, const int* query_start, const int* slots, int num_tokens, int num_seqs,
+                           int hidden, int mixes, cudaStream_t stream) {
+  if (num_tokens <= 0 || num_seqs <= 0) return 0;
+  if (hidden < 1 || mixes < 1) return TS_ERR_SIZE;
+  const int threads = hidden >= 256 ? 256 : 64;
+  if (dtype == TS_F32) {
+    ts_launch(shift_mix_kernel<float>, dim3(num_tokens), dim3(threads), 0, stream, (const float*)x, mu, (const float*)last,
+              (float*)out, positions, seq_of_token, query_start, slots, hidden, mixes);
+    ts_launch(shift_keep_kernel<float>, dim3(num_seqs), dim3(threads), 0, stream, (const float*)x, (float*)last, query_start,
+              slots, hidden);
+  } else if (dtype == TS_BF16) {
+    ts_launch(shift_mix_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(threads), 0, stream, (const __nv_bfloat16*)x, mu,
+              (const __nv_bfloat16*)last, (__nv_bfloat16*)out, positions, seq_of_token, query_start, slots, hidden, mixes);
+    ts_launch(shift_keep_kernel<__nv_bfloat16>, dim3(num_seqs), dim3(threads), 0, stream, (const __nv_bfloat16*)x,
+              (__nv_bfloat16*)last, query_start, slots, hidden);
+  } else {
+    return TS_ERR_DTYPE;
+  }
   return ts_launch_status();
 }

@@ -20,7 +20,7 @@ from ..cache.manager import GroupSpec
 from ..cache.storage import CachePlan, CacheStorage
 from ..config.registry import config_from_dir, lookup
 from ..models.decoder import DecoderModel
-from ..weights.loader import load_weights
+from ..weights.loader import checkpoint_index, load_weights
 from .batch import RequestSlice, StaticBatch, StepBatch, StepContext, Workspace, build_step_batch, skew_class
 
 STATUS_MESSAGES = {
@@ -50,6 +50,9 @@ def load_model(model_dir: str | Path, dtype: torch.dtype, device: torch.device |
     """Build the model ``config.json`` names and load ``model.safetensors`` into it."""
     device = torch.device(device) if device is not None else require_cuda()
     config = config_from_dir(model_dir)
+    fill = getattr(config, "with_tensor_shapes", None)
+    if fill is not None:  # a design may leave sizes to the shapes of its tensors
+        config = fill({name: tuple(entry[1]) for name, entry in checkpoint_index(model_dir).items()})
     model = lookup(config.architecture).build_model(config, dtype, device)
     model.config = config
     load_weights(model, model_dir)

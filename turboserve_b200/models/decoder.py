@@ -199,8 +199,10 @@ class DecoderModel:
             else:
                 from ..ops import kernels
 
-                updates = tuple(p for p in (pending if isinstance(pending, tuple) else (pending,)) if p is not None)
-                kernels.stream_norm(residual, updates, shift, None, None, num_rows=n, dtype=self.dtype)
+                from ..parts.base import pending_updates
+
+                updates, mult = pending_updates(pending)
+                kernels.stream_norm(residual, updates, shift, None, None, num_rows=n, dtype=self.dtype, mult=mult)
                 pending = block.forward(residual, None, ctx, storage.run_caches[run_index])
         rows = batch.num_logit_rows
         if rows == 0:

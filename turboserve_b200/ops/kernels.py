@@ -23,7 +23,7 @@ _ERRORS = {
     -4: "an argument was refused",
 }
 
-ACTIVATION_CODES = {"silu": 0, "gelu": 1, "gelu_pytorch_tanh": 2}
+ACTIVATION_CODES = {"silu": 0, "gelu": 1, "gelu_pytorch_tanh": 2, "clamped_swish": 3}
 
 
 class KernelError(RuntimeError):
@@ -132,8 +132,9 @@ def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, gain: torch.
 
 
 def act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str, num_tokens: int | None = None,
-            block: int = 0) -> None:
-    """``out[t, i] = act(gate[t, i]) * up[t, i]`` in fp32, rounded once.
+            block: int = 0, limit: float = 0.0, alpha: float = 0.0) -> None:
+    """``out[t, i] = act(gate[t, i]) * up[t, i]`` in fp32, rounded once; with ``clamped_swish``
+    ``g sigmoid(alpha g) (u + 1)`` for ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``.
 
     ``block == 0``: a row of ``gate_up`` is ``[gate | up]``. ``block > 0``: gate and up alternate
     in runs of ``block`` features (``[g 0..b-1 | u 0..b-1 | g b..2b-1 | ...]``).
@@ -145,9 +146,9 @@ def act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str, num_token
     if activation not in ACTIVATION_CODES:
         raise KernelError(f"act_mul: unknown activation {activation!r}")
     n = gate_up.shape[0] if num_tokens is None else num_tokens
-    fn = _fn("layer_ops", "ts_act_mul", [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    fn = _fn("layer_ops", "ts_act_mul", [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
     _check(fn(dtype_code(out.dtype), _ptr(gate_up), _ptr(out), n, inter, ACTIVATION_CODES[activation], int(block),
-              _stream()), "act_mul")
+              float(limit), float(alpha), _stream()), "act_mul")
 
 
 def rope_cache_write(qkv: torch.Tensor, bias: torch.Tensor | None, positions: torch.Tensor, seq_of_token: torch.Tensor,
@@ -186,6 +187,49 @@ def rope_cache_write(qkv: torch.Tensor, bias: torch.Tensor | None, positions: to
               _ptr(status), _stream()), "rope_cache_write")
 
 
+def head_norm_rope_write(qkv: torch.Tensor, q_gain: torch.Tensor | None, k_gain: torch.Tensor | None, eps: float,
+                         positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+                         k_pages: torch.Tensor | None, v_pages: torch.Tensor | None, num_tokens: int, num_heads: int,
+                         num_kv_heads: int, dim: int, vdim: int, inv_freq: torch.Tensor | None, rotary_dim: int,
+                         interleaved: bool, write_kv: bool, status: torch.Tensor | None = None) -> None:
+    """RMS norm per head of q and k (gains of ``dim`` floats shared by the heads, or ``None``), rotation of the first
+    ``rotary_dim`` elements (pairs ``(2i, 2i + 1)`` when ``interleaved``, else ``(i, i + rotary_dim / 2)``), and the
+    append of keys (``dim`` wide) and values (``vdim`` wide) to their pages; all in fp32, rounded once.
+
+    ``qkv`` rows are ``[num_heads * dim | num_kv_heads * dim | num_kv_heads * vdim]``; queries are changed in place."""
+    _need(qkv, None, "qkv"); _need(positions, torch.int32, "positions"); _need(seq_of_token, torch.int32, "seq_of_token")
+    _need(block_table, torch.int32, "block_table")
+    if qkv.dim() != 2 or qkv.shape[1] < (num_heads + num_kv_heads) * dim + num_kv_heads * vdim:
+        raise KernelError("head_norm_rope_write: qkv is narrower than its heads")
+    for name, gain in (("q_gain", q_gain), ("k_gain", k_gain)):
+        if gain is not None:
+            _need(gain, torch.float32, name)
+            if gain.numel() != dim:
+                raise KernelError(f"head_norm_rope_write: {name} must hold dim floats")
+    page_size = 1
+    if write_kv:
+        if k_pages is None or v_pages is None:
+            raise KernelError("head_norm_rope_write: pages are needed to write keys and values")
+        _need(k_pages, qkv.dtype, "k_pages"); _need(v_pages, qkv.dtype, "v_pages")
+        if (not k_pages.is_contiguous() or not v_pages.is_contiguous() or tuple(k_pages.shape[2:]) != (num_kv_heads, dim)
+                or tuple(v_pages.shape[2:]) != (num_kv_heads, vdim) or k_pages.shape[1] != v_pages.shape[1]):
+            raise KernelError("head_norm_rope_write: pages must be contiguous [pages, page_size, kv_heads, dim | vdim]")
+        page_size = k_pages.shape[1]
+    if rotary_dim:
+        if inv_freq is None:
+            raise KernelError("head_norm_rope_write: a rotation needs its frequencies")
+        _need(inv_freq, torch.float32, "inv_freq")
+        if inv_freq.numel() * 2 != rotary_dim:
+            raise KernelError("head_norm_rope_write: inv_freq must hold rotary_dim / 2 values")
+    fn = _fn("layer_ops", "ts_head_norm_rope_write",
+             [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+              c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(dtype_code(qkv.dtype), _ptr(qkv), qkv.stride(0), _ptr(q_gain), _ptr(k_gain), float(eps), _ptr(positions),
+              _ptr(seq_of_token), _ptr(block_table), block_table.stride(0), _ptr(k_pages), _ptr(v_pages), page_size,
+              num_tokens, num_heads, num_kv_heads, dim, vdim, _ptr(inv_freq), int(rotary_dim), 1 if interleaved else 0,
+              1 if write_kv else 0, _ptr(status), _stream()), "head_norm_rope_write")
+
+
 # ---------------------------------------------------------------------------------------
 # attention_generic.cu
 # ---------------------------------------------------------------------------------------
@@ -215,20 +259,45 @@ def paged_attention_generic(q: torch.Tensor, out: torch.Tensor, k_pages: torch.T
               _stream()), "paged_attention_generic")
 
 
+def paged_attention_capped(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                           block_table: torch.Tensor, seq_of_token: torch.Tensor, positions: torch.Tensor,
+                           num_tokens: int, num_heads: int, num_kv_heads: int, head_dim: int, v_dim: int,
+                           window: int | None, scale: float, softcap: float = 0.0, sink: bool = False,
+                           status: torch.Tensor | None = None) -> None:
+    """:func:`paged_attention_generic` with every option: value rows of ``v_dim`` elements, scores capped as
+    ``softcap * tanh(score / softcap)`` (0: uncapped), and a ``sink`` (one added to the softmax's denominator, as if
+    one more key scored 0 and had no value). ``out`` is ``[tokens, >= num_heads * v_dim]``."""
+    _need(q, None, "q"); _need(out, q.dtype, "out"); _need(k_pages, q.dtype, "k_pages"); _need(v_pages, q.dtype, "v_pages")
+    _need(block_table, torch.int32, "block_table"); _need(seq_of_token, torch.int32, "seq_of_token"); _need(positions, torch.int32, "positions")
+    if (not k_pages.is_contiguous() or not v_pages.is_contiguous() or tuple(k_pages.shape[2:]) != (num_kv_heads, head_dim)
+            or tuple(v_pages.shape[2:]) != (num_kv_heads, v_dim) or k_pages.shape[1] != v_pages.shape[1]):
+        raise KernelError("paged_attention: pages must be contiguous [pages, page_size, kv_heads, head_dim | v_dim]")
+    if q.shape[1] < num_heads * head_dim or out.shape[1] < num_heads * v_dim:
+        raise KernelError("paged_attention: q or out is narrower than its heads")
+    fn = _fn("attention_generic", "ts_paged_attention_capped",
+             [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p])
+    _check(fn(dtype_code(q.dtype), _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
+              _ptr(block_table), block_table.stride(0), _ptr(seq_of_token), _ptr(positions), num_tokens,
+              k_pages.shape[1], num_heads, num_kv_heads, head_dim, v_dim, int(window or 0), float(scale), float(softcap),
+              1 if sink else 0, _ptr(status), _stream()), "paged_attention_capped")
+
+
 # ---------------------------------------------------------------------------------------
 # stream_ops.cu
 # ---------------------------------------------------------------------------------------
 
-PLAIN_ACTIVATION_CODES = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+PLAIN_ACTIVATION_CODES = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "tanh": 3}
 
 
 def stream_norm(residual: torch.Tensor, deltas: tuple, shift: torch.Tensor | None, gain1: torch.Tensor | None,
                 out1: torch.Tensor | None, gain2: torch.Tensor | None = None, out2: torch.Tensor | None = None,
                 eps: float = 0.0, rows: torch.Tensor | None = None, num_rows: int | None = None,
-                dtype: torch.dtype | None = None) -> None:
+                dtype: torch.dtype | None = None, mult: float = 1.0) -> None:
     """``x = residual + deltas[0] + deltas[1] + shift`` in fp32 (each optional), written back unless
     ``rows`` selects rows; then ``out1 = x / rms(x) * gain1`` and, if given, ``out2 = x / rms(x) * gain2``.
-    With ``out1`` ``None`` only the sum is made (``dtype`` then names the deltas' type)."""
+    With ``out1`` ``None`` only the sum is made (``dtype`` then names the deltas' type). With ``mult``
+    other than 1 the sum is ``residual + mult * (deltas[0] + deltas[1]) + shift``."""
     _need(residual, torch.float32, "residual")
     hidden = residual.shape[-1]
     kind = out1.dtype if out1 is not None else (deltas[0].dtype if deltas else (dtype or torch.float32))
@@ -261,9 +330,46 @@ def stream_norm(residual: torch.Tensor, deltas: tuple, shift: torch.Tensor | Non
             raise KernelError("stream_norm: an output has too few rows")
     da = deltas[0] if len(deltas) > 0 else None
     db = deltas[1] if len(deltas) > 1 else None
-    fn = _fn("stream_ops", "ts_stream_norm", [c_int] + [c_void_p] * 9 + [c_int, c_int, c_float, c_void_p])
+    fn = _fn("stream_ops", "ts_stream_norm", [c_int] + [c_void_p] * 9 + [c_int, c_int, c_float, c_float, c_void_p])
     _check(fn(dtype_code(kind), _ptr(residual), _ptr(da), _ptr(db), _ptr(shift), _ptr(gain1), _ptr(out1), _ptr(gain2),
-              _ptr(out2), _ptr(rows), n, hidden, float(eps), _stream()), "stream_norm")
+              _ptr(out2), _ptr(rows), n, hidden, float(eps), float(mult), _stream()), "stream_norm")
+
+
+def norm_pair_mix(a: torch.Tensor, b: torch.Tensor, gain_a: torch.Tensor, gain_b: torch.Tensor, out: torch.Tensor,
+                  num_rows: int, eps: float, weight_a: float = 0.5, weight_b: float = 0.5) -> None:
+    """``out = weight_a * (a / rms(a) * gain_a) + weight_b * (b / rms(b) * gain_b)``: each input normed over its whole
+    row on its own (``eps`` inside the root), in fp32, rounded once."""
+    _need(a, None, "a"); _need(b, a.dtype, "b"); _need(out, a.dtype, "out")
+    _need(gain_a, torch.float32, "gain_a"); _need(gain_b, torch.float32, "gain_b")
+    hidden = a.shape[-1]
+    if (not a.is_contiguous() or not b.is_contiguous() or not out.is_contiguous() or b.shape[-1] != hidden or out.shape[-1] != hidden
+            or gain_a.numel() != hidden or gain_b.numel() != hidden or min(a.shape[0], b.shape[0], out.shape[0]) < num_rows):
+        raise KernelError("norm_pair_mix: shapes do not agree")
+    fn = _fn("stream_ops", "ts_norm_pair_mix",
+             [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_float, c_void_p])
+    _check(fn(dtype_code(a.dtype), _ptr(a), _ptr(b), _ptr(gain_a), _ptr(gain_b), _ptr(out), num_rows, hidden, float(eps),
+              float(weight_a), float(weight_b), _stream()), "norm_pair_mix")
+
+
+def shift_mix(x: torch.Tensor, mu: torch.Tensor, last: torch.Tensor, out: torch.Tensor, positions: torch.Tensor,
+              seq_of_token: torch.Tensor, query_start: torch.Tensor, slots: torch.Tensor, num_tokens: int, num_seqs: int) -> None:
+    """``out[t, s] = x[t] + (x[t - 1] - x[t]) * mu[s]`` for every row ``s`` of ``mu`` (float32 ``[mixes, hidden]``), side by
+    side in ``out`` ``[tokens, mixes * hidden]``. The row before a step's first token of a request is what ``last``
+    (``[slots, hidden]``, the activation type) kept; before position 0 it is zeros. ``last`` then takes every
+    request's last row of this step."""
+    _need(x, None, "x"); _need(out, x.dtype, "out"); _need(last, x.dtype, "last"); _need(mu, torch.float32, "mu")
+    for name, tensor in (("positions", positions), ("seq_of_token", seq_of_token), ("query_start", query_start), ("slots", slots)):
+        _need(tensor, torch.int32, name)
+    hidden = x.shape[-1]
+    mixes = mu.shape[0]
+    if (not x.is_contiguous() or not out.is_contiguous() or not last.is_contiguous() or not mu.is_contiguous() or mu.dim() != 2
+            or mu.shape[1] != hidden or out.shape[-1] != mixes * hidden or last.shape[-1] != hidden
+            or min(x.shape[0], out.shape[0], positions.numel(), seq_of_token.numel()) < num_tokens
+            or query_start.numel() < num_seqs + 1 or slots.numel() < num_seqs):
+        raise KernelError("shift_mix: shapes do not agree")
+    fn = _fn("stream_ops", "ts_shift_mix", [c_int] + [c_void_p] * 8 + [c_int] * 4 + [c_void_p])
+    _check(fn(dtype_code(x.dtype), _ptr(x), _ptr(mu), _ptr(last), _ptr(out), _ptr(positions), _ptr(seq_of_token),
+              _ptr(query_start), _ptr(slots), num_tokens, num_seqs, hidden, mixes, _stream()), "shift_mix", launches=2)
 
 
 def norm_add(residual: torch.Tensor, update: torch.Tensor | None, gain: torch.Tensor | None, copy: torch.Tensor | None,
@@ -292,7 +398,7 @@ def norm_add(residual: torch.Tensor, update: torch.Tensor | None, gain: torch.Te
 
 
 def activation(x: torch.Tensor, out: torch.Tensor, name: str, num_rows: int | None = None) -> None:
-    """``out = act(x)`` for contiguous rows; ``relu2`` (the square of relu), ``gelu_tanh`` or ``silu``."""
+    """``out = act(x)`` for contiguous rows; ``relu2`` (the square of relu), ``gelu_tanh``, ``silu`` or ``tanh``."""
     _need(x, None, "x"); _need(out, x.dtype, "out")
     if name not in PLAIN_ACTIVATION_CODES:
         raise KernelError(f"activation: unknown activation {name!r}")
@@ -458,6 +564,37 @@ def ssd_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_l
               int(num_tokens), _stream()), "ssd_scan")
 
 
+def selective_scan(x: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, bc: torch.Tensor, b_first: int, c_first: int,
+                   a_log: torch.Tensor, d_skip: torch.Tensor, z: torch.Tensor, state: torch.Tensor, out: torch.Tensor,
+                   query_start: torch.Tensor, slots: torch.Tensor, num_seqs: int, num_tokens: int) -> None:
+    """The state-space recurrence with a state per channel and a decay per channel and state index, in float32:
+
+    ``dt = softplus(dt_raw + dt_bias)``, ``S[c, n] = exp(dt[c] A[c, n]) S[c, n] + dt[c] x[c] B[n]`` with ``A = -exp(a_log)``,
+    ``y[c] = sum_n S[c, n] C[n] + d_skip[c] x[c]``, ``out = y * silu(z)`` rounded once.
+
+    ``x``, ``z`` and ``out`` are ``[tokens, inner]`` (columns of wider buffers are fine), ``dt_raw`` float32 contiguous
+    ``[tokens, inner]``, ``bc`` holds ``B`` from column ``b_first`` and ``C`` from ``c_first`` (``N`` each), ``a_log`` float32
+    ``[inner, N]``, ``state`` float32 ``[slots, inner, N]``."""
+    _need(x, None, "x"); _need(bc, x.dtype, "bc"); _need(z, x.dtype, "z"); _need(out, x.dtype, "out")
+    for name, tensor in (("dt_raw", dt_raw), ("dt_bias", dt_bias), ("a_log", a_log), ("d_skip", d_skip), ("state", state)):
+        _need(tensor, torch.float32, name)
+    _need(query_start, torch.int32, "query_start"); _need(slots, torch.int32, "slots")
+    inner, n_state = a_log.shape
+    if (x.shape[1] != inner or z.shape[1] != inner or out.shape[1] != inner or not dt_raw.is_contiguous() or dt_raw.shape[1] != inner
+            or dt_bias.numel() != inner or d_skip.numel() != inner or not a_log.is_contiguous() or not state.is_contiguous()
+            or tuple(state.shape[1:]) != (inner, n_state) or bc.shape[1] < max(b_first, c_first) + n_state
+            or any(t.stride(1) != 1 for t in (x, z, out, bc))):
+        raise KernelError("selective_scan: shapes do not agree")
+    if min(x.shape[0], z.shape[0], out.shape[0], bc.shape[0], dt_raw.shape[0]) < num_tokens or query_start.numel() < num_seqs + 1:
+        raise KernelError("selective_scan: fewer rows than asked for")
+    fn = _fn("ssd_ops", "ts_selective_scan",
+             [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p,
+              c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(dtype_code(x.dtype), _ptr(x), x.stride(0), _ptr(dt_raw), _ptr(dt_bias), _ptr(bc), bc.stride(0), int(b_first),
+              int(c_first), _ptr(a_log), _ptr(d_skip), _ptr(z), z.stride(0), _ptr(state), _ptr(out), out.stride(0),
+              _ptr(query_start), _ptr(slots), num_seqs, inner, n_state, _stream()), "selective_scan")
+
+
 def gated_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, num_tokens: int,
                      parts: int, eps: float) -> None:
     """``out = norm_parts(y * silu(z)) * weight``: ``y`` float32 ``[tokens, inner]``, ``z`` a view of ``inner`` columns."""
@@ -590,14 +727,18 @@ def retention_scratch_per_token(heads: int, dim: int, vdim: int) -> int:
 def retention_scan(qkv: torch.Tensor, q_first: int, k_first: int, v_first: int, decay: torch.Tensor,
                    inv_freq: torch.Tensor, rot: int, amplitude: float, key_scale: float, positions: torch.Tensor,
                    seq_of_token: torch.Tensor, query_start: torch.Tensor, slots: torch.Tensor, state: torch.Tensor,
-                   y: torch.Tensor, scratch: torch.Tensor, num_tokens: int, num_seqs: int, heads: int, dim: int, vdim: int) -> None:
+                   y: torch.Tensor, scratch: torch.Tensor, num_tokens: int, num_seqs: int, heads: int, dim: int, vdim: int,
+                   activation: str | None = None) -> None:
     """The decayed outer-product recurrence over the step's positions of every request.
 
     ``qkv`` rows hold q (``heads * dim`` from column ``q_first``), k (from ``k_first``) and v (``heads * vdim`` from
     ``v_first``) as projected; ``state`` is float32 ``[slots, heads, vdim, dim]``, ``y`` float32 ``[tokens, heads * vdim]``;
     ``scratch`` float32 with :func:`retention_scratch_per_token` floats per token. Two launches: the rotation of
-    q and k (fp32), then the scan."""
+    q and k (fp32), then the scan. With ``activation`` ``"silu"`` q, k and v pass it as they are read (then without a
+    rotation)."""
     _need(qkv, None, "qkv"); _need(decay, torch.float32, "decay"); _need(inv_freq, torch.float32, "inv_freq")
+    if activation not in (None, "silu") or (activation and rot):
+        raise KernelError("retention_scan: the activation is silu or none, and goes with no rotation")
     _need(state, torch.float32, "state"); _need(y, torch.float32, "y"); _need(scratch, torch.float32, "scratch")
     for name, tensor in (("positions", positions), ("seq_of_token", seq_of_token), ("query_start", query_start), ("slots", slots)):
         _need(tensor, torch.int32, name)
@@ -611,6 +752,13 @@ def retention_scan(qkv: torch.Tensor, q_first: int, k_first: int, v_first: int, 
         raise KernelError("retention_scan: fewer rows than asked for")
     if not scratch.is_contiguous() or scratch.numel() < num_tokens * retention_scratch_per_token(heads, dim, vdim):
         raise KernelError("retention_scan: the scratch is too small")
+    if activation:
+        fn = _fn("retention_ops", "ts_retention_scan_act",
+                 [c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_float, c_int] + [c_void_p] * 7 + [c_int] * 5 + [c_void_p])
+        _check(fn(dtype_code(qkv.dtype), _ptr(qkv), qkv.stride(0), int(q_first), int(k_first), int(v_first), _ptr(decay),
+                  float(key_scale), 1, _ptr(positions), _ptr(seq_of_token), _ptr(query_start), _ptr(slots), _ptr(state), _ptr(y),
+                  _ptr(scratch), num_tokens, num_seqs, heads, dim, vdim, _stream()), "retention_scan", launches=2)
+        return
     fn = _fn("retention_ops", "ts_retention_scan",
              [c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_float] + [c_void_p] * 7 +
              [c_int] * 5 + [c_void_p])
@@ -628,6 +776,72 @@ def head_norm_gate(y: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, num_t
     fn = _fn("retention_ops", "ts_head_norm_gate", [c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
     _check(fn(dtype_code(gate.dtype), _ptr(y), _ptr(gate), gate.stride(0), _ptr(out), num_tokens, heads, vdim, float(eps),
               _stream()), "head_norm_gate")
+
+
+def part_norm_gate(y: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, num_tokens: int, parts: int, width: int, eps: float,
+                   weight: torch.Tensor | None = None, gate_activation: str = "silu") -> None:
+    """A row of ``y`` (float32 ``[tokens, parts * width]``) cut into ``parts`` equal parts, each divided by its own root
+    mean square (``eps`` inside the root), times ``weight`` (float32, a row's worth, or ``None``), times
+    ``silu(gate)`` or ``sigmoid(gate)``. ``parts`` = heads norms every head alone, ``parts`` = 1 the whole row."""
+    _need(y, torch.float32, "y"); _need(gate, None, "gate"); _need(out, gate.dtype, "out")
+    if gate_activation not in ("silu", "sigmoid"):
+        raise KernelError("part_norm_gate: the gate's activation is silu or sigmoid")
+    row = parts * width
+    if not y.is_contiguous() or not out.is_contiguous() or y.shape[1] != row or out.shape[1] != row or gate.shape[1] < row:
+        raise KernelError("part_norm_gate: shapes do not agree")
+    if weight is not None:
+        _need(weight, torch.float32, "weight")
+        if weight.numel() != row or not weight.is_contiguous():
+            raise KernelError("part_norm_gate: the weight must hold a row's worth of floats")
+    fn = _fn("retention_ops", "ts_part_norm_gate",
+             [c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p])
+    _check(fn(dtype_code(gate.dtype), _ptr(y), _ptr(gate), gate.stride(0), _ptr(out), num_tokens, parts, width, float(eps),
+              _ptr(weight), 1 if gate_activation == "sigmoid" else 0, _stream()), "part_norm_gate")
+
+
+def chosen_decay_scratch_per_token(heads: int, dim: int, vdim: int) -> int:
+    """Floats of scratch :func:`chosen_decay_scan` needs per token of a step (q, k, the decays and the values, in fp32)."""
+    fn = _fn("retention_ops", "ts_chosen_decay_scratch_per_token", [c_int, c_int, c_int])
+    return int(fn(heads, dim, vdim))
+
+
+def chosen_decay_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, bonus: torch.Tensor, decay_raw: torch.Tensor,
+                      decay_bias: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, query_start: torch.Tensor,
+                      slots: torch.Tensor, state: torch.Tensor, y: torch.Tensor, scratch: torch.Tensor, num_tokens: int,
+                      num_seqs: int, heads: int, dim: int, vdim: int) -> None:
+    """The recurrence with a decay the input chooses, per head, in float32:
+
+    ``y_t = (S_{t-1} + diag(u) k_t v_t^T)^T q_t``, then ``S_t = diag(w_t) S_{t-1} + k_t v_t^T`` with
+    ``w_t = exp(-exp(decay_raw_t + decay_bias))`` per key channel and ``u`` the ``bonus`` ``[heads, dim]``.
+
+    ``q``, ``k`` (``[tokens, heads * dim]``) and ``v`` (``[tokens, heads * vdim]``) are views of columns of ONE buffer (the same
+    row stride); ``decay_raw`` float32 ``[tokens, heads * dim]``; ``state`` float32 ``[slots, heads, vdim, dim]``; ``y`` float32
+    ``[tokens, heads * vdim]``; ``scratch`` float32 with :func:`chosen_decay_scratch_per_token` floats per token."""
+    for name, tensor in (("q", q), ("k", k), ("v", v)):
+        _need(tensor, q.dtype, name)
+    for name, tensor in (("bonus", bonus), ("decay_raw", decay_raw), ("decay_bias", decay_bias), ("state", state), ("y", y), ("scratch", scratch)):
+        _need(tensor, torch.float32, name)
+    for name, tensor in (("positions", positions), ("seq_of_token", seq_of_token), ("query_start", query_start), ("slots", slots)):
+        _need(tensor, torch.int32, name)
+    size = q.element_size()
+    if not (q.stride(0) == k.stride(0) == v.stride(0)) or q.shape[1] != heads * dim or k.shape[1] != heads * dim or v.shape[1] != heads * vdim:
+        raise KernelError("chosen_decay_scan: q, k and v must be columns of one buffer, heads * dim and heads * vdim wide")
+    k_first, v_first = (k.data_ptr() - q.data_ptr()) // size, (v.data_ptr() - q.data_ptr()) // size
+    if min(k_first, v_first) < 0 or (k.data_ptr() - q.data_ptr()) % size or (v.data_ptr() - q.data_ptr()) % size:
+        raise KernelError("chosen_decay_scan: k and v must lie behind q in the buffer")
+    if bonus.numel() != heads * dim or decay_bias.numel() != heads * dim or not decay_raw.is_contiguous() or decay_raw.shape[1] != heads * dim:
+        raise KernelError("chosen_decay_scan: bonus, decay_bias and the rows of decay_raw hold heads * dim floats")
+    if not state.is_contiguous() or tuple(state.shape[1:]) != (heads, vdim, dim) or not y.is_contiguous() or y.shape[1] != heads * vdim:
+        raise KernelError("chosen_decay_scan: state must be [slots, heads, vdim, dim] and y [tokens, heads * vdim]")
+    if min(q.shape[0], decay_raw.shape[0], y.shape[0], positions.numel(), seq_of_token.numel()) < num_tokens or query_start.numel() < num_seqs + 1:
+        raise KernelError("chosen_decay_scan: fewer rows than asked for")
+    if not scratch.is_contiguous() or scratch.numel() < num_tokens * chosen_decay_scratch_per_token(heads, dim, vdim):
+        raise KernelError("chosen_decay_scan: the scratch is too small")
+    fn = _fn("retention_ops", "ts_chosen_decay_scan",
+             [c_int, c_void_p, c_longlong, c_int, c_int, c_int] + [c_void_p] * 10 + [c_int] * 5 + [c_void_p])
+    _check(fn(dtype_code(q.dtype), _ptr(q), q.stride(0), 0, int(k_first), int(v_first), _ptr(bonus), _ptr(decay_raw),
+              _ptr(decay_bias), _ptr(positions), _ptr(seq_of_token), _ptr(query_start), _ptr(slots), _ptr(state), _ptr(y),
+              _ptr(scratch), num_tokens, num_seqs, heads, dim, vdim, _stream()), "chosen_decay_scan", launches=2)
 
 
 # ---------------------------------------------------------------------------------------

@@ -4,8 +4,9 @@ The rule is explicit, measured on B200 (graph-timed, every weight read from HBM)
 fallback chain:
 
 * float32: the FFMA kernel (``gemm_simt.cu``), always. No TF32, no tensor cores.
-* bfloat16 with an inner size that is not a multiple of 8: the FFMA kernel (rows of such a
-  matrix are not 16-byte aligned, which every tensor-core path needs).
+* bfloat16 with an inner size that is not a multiple of 8, or with an input or output that is a
+  range of columns of a wider buffer whose rows do not start on 16-byte boundaries: the FFMA
+  kernel (every tensor-core path needs aligned rows).
 * bfloat16, at most :data:`TC_MAX_ROWS` rows and at least :data:`TC_MIN_FEATURES` output
   features (the gate/up projection, the output head): the TMA + tcgen05 kernel
   (``gemm_tc.cu``): 6.0 to 6.8 TB/s, ahead of cuBLAS and of the register-streaming kernel.
@@ -39,6 +40,11 @@ TC_MAX_ROWS = 64
 TC_MIN_FEATURES = 16384
 
 
+def _ragged(t: torch.Tensor) -> bool:
+    """Columns of a wider buffer whose rows do not start on 16-byte boundaries (the FFMA kernel takes those)."""
+    return (t.stride(0) * t.element_size()) % 16 != 0 or t.data_ptr() % 16 != 0
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None = None,
            rows: int | None = None, ctx=None, early_trigger: bool = True) -> torch.Tensor:
     """``out[:rows] = x[:rows] @ weight.T (+ bias)``; ``bias`` is float32.
@@ -51,7 +57,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: torch
     if m == 0:
         return out
     n, k = weight.shape
-    if x.dtype == torch.float32 or k % 8 != 0:
+    if x.dtype == torch.float32 or k % 8 != 0 or _ragged(x) or _ragged(out):
         kernels.gemm_simt(x, weight, out, bias, m)
         return out
     if m <= TC_MAX_ROWS and n >= TC_MIN_FEATURES:
@@ -97,13 +103,14 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> tuple[torch.Tens
 
 
 def gated_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None, activation: str,
-                 block: int, rows: int | None = None, ctx=None) -> torch.Tensor:
+                 block: int, rows: int | None = None, ctx=None, limit: float = 0.0, alpha: float = 0.0) -> torch.Tensor:
     """``out[:rows] = act(x gate^T) * (x up^T)`` for a ``weight`` made by :func:`interleave_gate_up`.
 
     bfloat16, at most :data:`TC_MAX_ROWS` rows and an interleaved weight: one tcgen05 kernel whose
     epilogue applies the activation (3.6 µs and a launch less per layer of a decode step; the
     result equals the two-kernel path bit for bit, since gate and up are rounded to bfloat16
     before the activation in both). Everything else: :func:`linear`, then the activation kernel.
+    ``limit`` and ``alpha`` are the constants of the ``clamped_swish`` form.
     """
     m = x.shape[0] if rows is None else rows
     if m == 0:
@@ -112,9 +119,9 @@ def gated_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bias:
     if x.dtype == torch.bfloat16 and block == GATE_BLOCK and k % 8 == 0 and m <= TC_MAX_ROWS:
         from . import tc
 
-        tc.gemm_tc_gated(x, weight, out, bias, activation, m, status=ctx.status if ctx is not None else None)
+        tc.gemm_tc_gated(x, weight, out, bias, activation, m, status=ctx.status if ctx is not None else None, limit=limit, alpha=alpha)
         return out
     both = ctx.buffer("mlp.gate_up", (x.shape[0], n)) if ctx is not None else torch.empty(x.shape[0], n, dtype=x.dtype, device=x.device)
     linear(x, weight, both, bias, m, ctx)
-    kernels.act_mul(both, out, activation, m, block=block)
+    kernels.act_mul(both, out, activation, m, block=block, limit=limit, alpha=alpha)
     return out

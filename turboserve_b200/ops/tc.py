@@ -2,7 +2,7 @@
 
 from __future__ import annotations
 
-from ctypes import c_int, c_longlong, c_void_p
+from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
 
@@ -58,9 +58,10 @@ GATE_BLOCK = 64
 
 
 def gemm_tc_gated(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: torch.Tensor | None, activation: str,
-                  m: int | None = None, status: torch.Tensor | None = None) -> None:
+                  m: int | None = None, status: torch.Tensor | None = None, limit: float = 0.0, alpha: float = 0.0) -> None:
     """``out[:m] = act(a gate^T) * (a up^T)`` in one kernel; ``w`` is ``[2 * I, k]`` with gate and up
-    rows alternating in runs of :data:`GATE_BLOCK`, ``out`` is ``[m, I]``. At most 128 rows."""
+    rows alternating in runs of :data:`GATE_BLOCK`, ``out`` is ``[m, I]``. At most 128 rows. ``limit`` and ``alpha`` are
+    the constants of the ``clamped_swish`` form (:func:`turboserve_b200.ops.kernels.act_mul`)."""
     rows = a.shape[0] if m is None else m
     n, k = w.shape
     _need(a, torch.bfloat16, "a"); _need(w, torch.bfloat16, "w"); _need(out, None, "out")
@@ -74,6 +75,7 @@ def gemm_tc_gated(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: tor
             raise KernelError("gemm_tc_gated: bias length does not match the weight")
     fn = _fn("gemm_tc", "ts_gemm_tc_gated",
              [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int,
-              c_int, c_void_p, c_void_p])
+              c_int, c_float, c_float, c_void_p, c_void_p])
     _check(fn(kernels.dtype_code(out.dtype), _ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out),
-              out.stride(0), rows, n, k, kernels.ACTIVATION_CODES[activation], _ptr(status), _stream()), "gemm_tc_gated")
+              out.stride(0), rows, n, k, kernels.ACTIVATION_CODES[activation], float(limit), float(alpha), _ptr(status),
+              _stream()), "gemm_tc_gated")

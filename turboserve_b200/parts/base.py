@@ -123,6 +123,28 @@ UNDECLARED_SCRATCH_WIDTHS = 4
 """Hidden sizes of scratch per token assumed for a part that does not declare its own."""
 
 
+class ScaledUpdates(tuple):
+    """Updates a block leaves pending that enter the stream times a factor: ``stream += mult * sum(updates)``.
+
+    Whoever adds pending updates (the next norm, the final norm, a block that sums at once) reads ``mult``; a plain
+    tuple or a single tensor stands for a factor of one."""
+
+    mult: float = 1.0
+
+    def __new__(cls, items, mult: float = 1.0):
+        self = super().__new__(cls, tuple(items))
+        self.mult = float(mult)
+        return self
+
+
+def pending_updates(pending) -> tuple[tuple, float]:
+    """What a block left pending as ``(updates, mult)``, whatever form it was handed on in."""
+    if pending is None:
+        return (), 1.0
+    items = pending if isinstance(pending, (tuple, list)) else (pending,)
+    return tuple(p for p in items if p is not None), float(getattr(pending, "mult", 1.0))
+
+
 class Mixer(Part):
     """Mixes information between positions of a sequence.
 

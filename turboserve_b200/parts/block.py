@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import FeedForward, Mixer, Norm, register_block
+from .base import FeedForward, Mixer, Norm, ScaledUpdates, pending_updates, register_block
 
 
 class PreNormBlock:
@@ -36,12 +36,15 @@ class ParallelBlock:
     Both branches' outputs are handed on as a pair of pending updates; the next norm's kernel adds
     both into the fp32 residual (and a stream shift, if the next run brings one) and, when both
     norms are RMS norms with one ``eps``, writes both normed inputs in the same pass. A layer
-    without a feed-forward has one branch.
+    without a feed-forward has one branch. With ``residual_mult`` ``m`` other than 1 the layer is
+    ``h += m * (mixer(norm1(h)) + ff(norm2(h)))``: the factor travels with the pending updates.
     """
 
     takes_shift = True
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward | None, mixer_norm: Norm, feed_forward_norm: Norm | None) -> None:
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward | None, mixer_norm: Norm, feed_forward_norm: Norm | None,
+                 residual_mult: float = 1.0) -> None:
+        self.residual_mult = float(residual_mult)
         self.mixer = mixer
         self.feed_forward = feed_forward
         self.mixer_norm = mixer_norm
@@ -54,7 +57,7 @@ class ParallelBlock:
         for_mixer = ctx.buffer("block.normed", (n, hidden))
         if self.feed_forward is None:
             self.mixer_norm.forward(residual, pending, for_mixer, ctx, shift=shift)
-            return self.mixer.forward(for_mixer, ctx, cache)
+            return self._scaled((self.mixer.forward(for_mixer, ctx, cache),))
         for_ff = ctx.buffer("block.normed_ff", (n, hidden))
         pair = getattr(self.mixer_norm, "forward_pair", None)
         if pair is not None and getattr(self.feed_forward_norm, "eps", None) == getattr(self.mixer_norm, "eps", 0):
@@ -63,7 +66,12 @@ class ParallelBlock:
             self.mixer_norm.forward(residual, pending, for_mixer, ctx, shift=shift)
             self.feed_forward_norm.forward(residual, None, for_ff, ctx)
         mixed = self.mixer.forward(for_mixer, ctx, cache)
-        return mixed, self.feed_forward.forward(for_ff, ctx)
+        return self._scaled((mixed, self.feed_forward.forward(for_ff, ctx)))
+
+    def _scaled(self, updates: tuple):
+        if self.residual_mult == 1.0:
+            return updates if len(updates) > 1 else updates[0]
+        return ScaledUpdates(updates, self.residual_mult)
 
 
 class OutputNormBlock:
@@ -95,8 +103,8 @@ class OutputNormBlock:
 
         n, hidden = ctx.batch.num_tokens, residual.shape[-1]
         if pending is not None:  # what a block of another kind before this one left to be added
-            updates = tuple(p for p in (pending if isinstance(pending, tuple) else (pending,)) if p is not None)
-            kernels.stream_norm(residual, updates, None, None, None, num_rows=n, dtype=ctx.dtype)
+            updates, mult = pending_updates(pending)
+            kernels.stream_norm(residual, updates, None, None, None, num_rows=n, dtype=ctx.dtype, mult=mult)
             ctx.stream_copy = None
         if ctx.dtype == torch.float32:
             x = copy = None

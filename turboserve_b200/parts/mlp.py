@@ -1,4 +1,5 @@
-"""Dense gated feed-forward: ``down(act(gate(x)) * up(x))``.
+"""Dense gated feed-forward: ``down(act(gate(x)) * up(x))``, or with ``clamped_swish``
+``down(g sigmoid(alpha g) (u + 1))`` for ``g = min(gate(x), limit)``, ``u = clamp(up(x), -limit, limit)``.
 
 Gate and up projections are kept as one ``[2 * intermediate, hidden]`` matrix so the step runs
 one product for both (the reference runs two, ``src/turboserve/engine/model/layers.py:412-440``);
@@ -25,6 +26,11 @@ class GatedMLP(FeedForward):
         self.activation = str(spec.get("activation", "silu"))
         if self.activation not in kernels.ACTIVATION_CODES:
             raise ValueError(f"activation {self.activation!r} is not implemented; known: {sorted(kernels.ACTIVATION_CODES)}")
+        self.limit, self.alpha = float(spec.get("limit", 0.0)), float(spec.get("alpha", 1.702))
+        """Constants of ``clamped_swish``: ``g sigmoid(alpha g) (u + 1)`` with ``g = min(gate, limit)`` and
+        ``u = clamp(up, -limit, limit)``; other activations ignore them."""
+        if self.activation == "clamped_swish" and not self.limit > 0.0:
+            raise ValueError("the clamped activation needs a positive 'limit'")
         self.has_bias = bool(spec.get("bias", False))
         self.names = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight", **dict(spec.get("names") or {})}
         """The three matrices' local names in the checkpoint."""
@@ -63,7 +69,8 @@ class GatedMLP(FeedForward):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         n = ctx.batch.num_tokens
         hidden = ctx.buffer("mlp.hidden", (n, self.intermediate_size))
-        gated_linear(x, self.gate_up, hidden, self.gate_up_bias, self.activation, self.gate_block, n, ctx)
+        gated_linear(x, self.gate_up, hidden, self.gate_up_bias, self.activation, self.gate_block, n, ctx,
+                     limit=self.limit, alpha=self.alpha)
         out = ctx.buffer("mlp.out", (n, self.hidden_size))
         linear(hidden, self.down, out, self.down_bias, n, ctx)
         return out

@@ -47,7 +47,7 @@ class RoutedExperts(FeedForward):
         self.groups, self.keep = int(spec.get("groups", 1)), int(spec.get("keep", 1))
         self.ff = int(spec["intermediate_size"])
         self.activation = str(spec.get("activation", "silu"))
-        if self.activation not in kernels.ACTIVATION_CODES:
+        if self.activation not in kernels.ACTIVATION_CODES or kernels.ACTIVATION_CODES[self.activation] > 2:  # the experts' kernels take act(gate) * up only
             raise ValueError(f"activation {self.activation!r} is not implemented; known: {sorted(kernels.ACTIVATION_CODES)}")
         if not 1 <= self.top <= min(self.experts, 32):
             raise ValueError(f"top must be between 1 and min(experts, 32), got {self.top} of {self.experts}")

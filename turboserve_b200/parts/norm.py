@@ -13,7 +13,7 @@ import torch
 
 from ..config.model_spec import PartSpec
 from ..ops import kernels
-from .base import Norm, ParamSpec, register_norm
+from .base import Norm, ParamSpec, pending_updates, register_norm
 
 
 class RMSNorm(Norm):
@@ -21,7 +21,8 @@ class RMSNorm(Norm):
     added once in float32 when the weights are bound); ``tensor`` (the weight's local name).
 
     ``delta`` may be one update, a pair of them (the two branches of a layer whose mixer and
-    feed-forward run side by side) or ``None``; ``shift`` a float32 vector that is added to every
+    feed-forward run side by side), :class:`~turboserve_b200.parts.base.ScaledUpdates` (updates that enter the
+    sum times a factor) or ``None``; ``shift`` a float32 vector that is added to every
     row as well. :meth:`forward_pair` norms the same sum with a second norm's gain in the same pass.
     """
 
@@ -46,26 +47,21 @@ class RMSNorm(Norm):
     def scratch_per_token(self) -> int:
         return 0  # it writes into the block's buffer
 
-    @staticmethod
-    def _updates(delta) -> tuple:
-        if delta is None:
-            return ()
-        return tuple(d for d in delta if d is not None) if isinstance(delta, (tuple, list)) else (delta,)
-
     def forward(self, residual, delta, out, ctx, shift=None):
-        updates = self._updates(delta)
-        if len(updates) <= 1 and shift is None:
+        updates, mult = pending_updates(delta)
+        if len(updates) <= 1 and shift is None and mult == 1.0:
             kernels.add_rmsnorm(residual, updates[0] if updates else None, self.gain, self.eps, out, None, ctx.batch.num_tokens)
         else:
-            kernels.stream_norm(residual, updates, shift, self.gain, out, eps=self.eps, num_rows=ctx.batch.num_tokens)
+            kernels.stream_norm(residual, updates, shift, self.gain, out, eps=self.eps, num_rows=ctx.batch.num_tokens, mult=mult)
         return out
 
     def forward_pair(self, residual, delta, other: "RMSNorm", out, out_other, ctx, shift=None):
         """Both norms of one sum: ``out`` with this norm's gain, ``out_other`` with ``other``'s (same ``eps``)."""
         if other.eps != self.eps:
             raise ValueError("forward_pair needs two norms with one eps")
-        kernels.stream_norm(residual, self._updates(delta), shift, self.gain, out, other.gain, out_other, eps=self.eps,
-                            num_rows=ctx.batch.num_tokens)
+        updates, mult = pending_updates(delta)
+        kernels.stream_norm(residual, updates, shift, self.gain, out, other.gain, out_other, eps=self.eps,
+                            num_rows=ctx.batch.num_tokens, mult=mult)
         return out, out_other
 
     def forward_output(self, residual, update, mult: float, copy, ctx):
@@ -75,11 +71,11 @@ class RMSNorm(Norm):
         return copy
 
     def forward_rows(self, residual, delta, rows, num_rows, out, ctx):
-        updates = self._updates(delta)
-        if len(updates) <= 1:
+        updates, mult = pending_updates(delta)
+        if len(updates) <= 1 and mult == 1.0:
             kernels.add_rmsnorm(residual, updates[0] if updates else None, self.gain, self.eps, out, rows, num_rows)
         else:
-            kernels.stream_norm(residual, updates, None, self.gain, out, eps=self.eps, rows=rows, num_rows=num_rows)
+            kernels.stream_norm(residual, updates, None, self.gain, out, eps=self.eps, rows=rows, num_rows=num_rows, mult=mult)
         return out
 
 

@@ -12,7 +12,13 @@ side are multiplied by ``silu(Wg h)`` and projected by ``Wo``. A request keeps `
 in its state slot (``[heads, vdim, dim]``); one kernel runs prompts, portions of them and single tokens.
 
 Sizes and constants are parameters: ``heads``, ``dim``, ``vdim``, ``decay`` (one per head), ``rot``, ``eps``;
-``names`` maps the roles ``q k v g o`` to the checkpoint's local tensor names.
+``names`` maps the roles ``q k v g o norm`` to the checkpoint's local tensor names.
+
+The lightning-attention form is the same recurrence with other constants around it, each a parameter:
+``activation`` (``"silu"``: q, k and v pass it as the scan reads them; then without a rotation), ``key_scale``
+(what k is multiplied by; default ``dim^-1/2``), ``norm`` (``"heads"``: every head alone, ``"row"``: the heads side by
+side as one row), ``norm_weight`` (a weight of ``heads * vdim`` values on the normed row) and ``gate`` (``"silu"`` or
+``"sigmoid"``).
 """
 
 from __future__ import annotations
@@ -25,7 +31,8 @@ from ..ops.linear import linear
 from .base import Mixer, ParamSpec, StateNeed, register_mixer
 from .rope import scaled_rotary_frequencies
 
-DEFAULT_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "g": "g_proj.weight", "o": "o_proj.weight"}
+DEFAULT_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "g": "g_proj.weight", "o": "o_proj.weight",
+                 "norm": "norm.weight"}
 
 
 class Retention(Mixer):
@@ -53,6 +60,16 @@ class Retention(Mixer):
             self.inv_freq = freq.to(device)
         else:
             self.inv_freq, self.amplitude = torch.zeros(0, dtype=torch.float32, device=device), 1.0
+        self.activation = spec.get("activation") or None
+        if self.activation not in (None, "silu") or (self.activation and self.rot):
+            raise ValueError("retention's activation is 'silu' or none, and goes with no rotation")
+        self.key_scale = float(spec.get("key_scale", self.dim ** -0.5))
+        self.norm_over, self.gate = str(spec.get("norm", "heads")), str(spec.get("gate", "silu"))
+        if self.norm_over not in ("heads", "row") or self.gate not in ("silu", "sigmoid"):
+            raise ValueError("retention norms 'heads' or the 'row', and gates with 'silu' or 'sigmoid'")
+        self.has_norm_weight = bool(spec.get("norm_weight", False))
+        self.plain = self.norm_over == "heads" and self.gate == "silu" and not self.has_norm_weight
+        self.norm_w: torch.Tensor | None = None
         self.names = {**DEFAULT_NAMES, **dict(spec.get("names") or {})}
         self.dtype = dtype
         self.qk_width, self.v_width = self.heads * self.dim, self.heads * self.vdim
@@ -78,13 +95,18 @@ class Retention(Mixer):
 
     def param_specs(self) -> list[ParamSpec]:
         n, h = self.names, self.hidden_size
-        return [ParamSpec(n["q"], (self.qk_width, h)), ParamSpec(n["k"], (self.qk_width, h)), ParamSpec(n["v"], (self.v_width, h)),
-                ParamSpec(n["g"], (self.v_width, h)), ParamSpec(n["o"], (h, self.v_width))]
+        specs = [ParamSpec(n["q"], (self.qk_width, h)), ParamSpec(n["k"], (self.qk_width, h)), ParamSpec(n["v"], (self.v_width, h)),
+                 ParamSpec(n["g"], (self.v_width, h)), ParamSpec(n["o"], (h, self.v_width))]
+        if self.has_norm_weight:
+            specs.append(ParamSpec(n["norm"], (self.v_width,), role="gain", init="one_plus_normal"))
+        return specs
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         n = self.names
         self.proj = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]], tensors[n["g"]]], dim=0).contiguous()
         self.out_w = tensors[n["o"]].contiguous()
+        if self.has_norm_weight:
+            self.norm_w = tensors[n["norm"]].contiguous()
 
     def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
         batch = ctx.batch
@@ -94,10 +116,17 @@ class Retention(Mixer):
         y = ctx.buffer("retention.y", (n, self.v_width), torch.float32)
         scratch = ctx.buffer("retention.scratch", (n * self.scan_scratch,), torch.float32)
         kernels.retention_scan(projected, 0, self.qk_width, 2 * self.qk_width, self.decay, self.inv_freq, self.rot,
-                               self.amplitude, self.dim ** -0.5, batch.positions, batch.seq_of_token, batch.query_start_loc,
-                               batch.state_slots, cache.states[0], y, scratch, n, batch.num_seqs, self.heads, self.dim, self.vdim)
+                               self.amplitude, self.key_scale, batch.positions, batch.seq_of_token, batch.query_start_loc,
+                               batch.state_slots, cache.states[0], y, scratch, n, batch.num_seqs, self.heads, self.dim, self.vdim,
+                               activation=self.activation)
         gated = ctx.buffer("retention.gated", (n, self.v_width))
-        kernels.head_norm_gate(y, projected[:, 2 * self.qk_width + self.v_width:], gated, n, self.heads, self.vdim, self.eps)
+        gate = projected[:, 2 * self.qk_width + self.v_width:]
+        if self.plain:
+            kernels.head_norm_gate(y, gate, gated, n, self.heads, self.vdim, self.eps)
+        elif self.norm_over == "heads":
+            kernels.part_norm_gate(y, gate, gated, n, self.heads, self.vdim, self.eps, self.norm_w, self.gate)
+        else:
+            kernels.part_norm_gate(y, gate, gated, n, 1, self.v_width, self.eps, self.norm_w, self.gate)
         out = ctx.buffer("retention.out", (n, self.hidden_size))
         linear(gated, self.out_w, out, None, n, ctx)
         return out

@@ -1,0 +1,113 @@
+"""Grouped-query softmax attention with normed heads, capped scores and a sink in the denominator.
+
+Per token ``q = Wq h`` (``heads x dim``), ``k = Wk h`` (``kv_heads x dim``), ``v = Wv h`` (``kv_heads x vdim``), no
+biases; query head ``j`` reads key/value head ``j // (heads / kv_heads)``. Options, each a parameter:
+
+* ``qk_norm``: every head of ``q`` and of ``k`` is divided by its root mean square over ``dim`` (``eps`` inside the
+  root) and multiplied by a weight of ``dim`` values that all heads share (one for queries, one for keys), before
+  the rotation;
+* ``rot``: the first ``rot.dims`` elements of every head of ``q`` and ``k`` turn by ``position * base^(-2i / dims)``;
+  pair ``i`` is elements ``(2i, 2i + 1)`` when ``rot.interleaved``, else ``(i, i + dims / 2)``;
+* ``softcap``: ``score = cap * tanh(scale * (q . k) / cap)``;
+* ``sink``: the softmax's denominator is one larger, ``p_j = exp(s_j) / (1 + sum exp(s_j))``: a key that scores 0
+  and has no value;
+* ``window``: the keys seen, the query's own included (``None``: all up to its position).
+
+Norm, rotation and the append of keys and values to the request's pages are one kernel in fp32; scores, the
+softmax and its sums are fp32 in the attention kernel. ``names`` maps the roles ``q k v o q_norm k_norm`` to the
+checkpoint's local tensor names.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..config.model_spec import PartSpec
+from ..ops import kernels
+from ..ops.linear import linear
+from .base import Mixer, PagedKVNeed, ParamSpec, register_mixer
+
+DEFAULT_NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+                 "q_norm": "q_norm.weight", "k_norm": "k_norm.weight"}
+
+
+class SinkAttention(Mixer):
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, hidden_size: int, dtype: torch.dtype, device: torch.device | str,
+                 position: PartSpec | None = None, shares_cache: bool = False) -> None:
+        if shares_cache:
+            raise ValueError("this attention keeps pages of its own")
+        self.hidden_size = int(hidden_size)
+        self.heads, self.kv_heads = int(spec["heads"]), int(spec["kv_heads"])
+        self.dim, self.vdim = int(spec["dim"]), int(spec.get("vdim") or spec["dim"])
+        if self.heads % self.kv_heads:
+            raise ValueError(f"heads ({self.heads}) must be a multiple of kv_heads ({self.kv_heads})")
+        if not 1 <= self.dim <= 256 or not 1 <= self.vdim <= 256:
+            raise ValueError(f"dim and vdim must lie between 1 and 256, got {self.dim} and {self.vdim}")
+        self.scale = float(spec.get("scale", self.dim ** -0.5))
+        self.softcap = float(spec.get("softcap") or 0.0)
+        self.sink = bool(spec.get("sink", False))
+        self.qk_norm = bool(spec.get("qk_norm", False))
+        self.eps = float(spec.get("eps", 1e-6))
+        window = spec.get("window")
+        self.window = int(window) if window else None
+        rot = dict(spec.get("rot") or {})
+        self.rot = int(rot.get("dims", 0))
+        self.interleaved = bool(rot.get("interleaved", False))
+        if self.rot > self.dim or self.rot % 2:
+            raise ValueError(f"the rotation covers {self.rot} of {self.dim} elements; it must be even and fit")
+        self.inv_freq = None
+        if self.rot:
+            index = torch.arange(self.rot // 2, dtype=torch.float64)
+            self.inv_freq = (float(rot["base"]) ** (-2.0 * index / self.rot)).to(torch.float32).to(device)
+        self.names = {**DEFAULT_NAMES, **dict(spec.get("names") or {})}
+        self.dtype = dtype
+        self.q_width, self.k_width, self.v_width = self.heads * self.dim, self.kv_heads * self.dim, self.kv_heads * self.vdim
+        self.qkv_width = self.q_width + self.k_width + self.v_width
+        self.qkv: torch.Tensor | None = None
+        self.out_w: torch.Tensor | None = None
+        self.q_gain: torch.Tensor | None = None
+        self.k_gain: torch.Tensor | None = None
+
+    def cache_need(self) -> PagedKVNeed:
+        return PagedKVNeed(self.kv_heads, self.dim, self.window, self.vdim)
+
+    def scratch_per_token(self) -> int:
+        return self.qkv_width + self.heads * self.vdim + self.hidden_size
+
+    def param_specs(self) -> list[ParamSpec]:
+        n, h = self.names, self.hidden_size
+        specs = [ParamSpec(n["q"], (self.q_width, h)), ParamSpec(n["k"], (self.k_width, h)), ParamSpec(n["v"], (self.v_width, h))]
+        if self.qk_norm:
+            specs += [ParamSpec(n["q_norm"], (self.dim,), role="gain", init="one_plus_normal"),
+                      ParamSpec(n["k_norm"], (self.dim,), role="gain", init="one_plus_normal")]
+        specs.append(ParamSpec(n["o"], (h, self.heads * self.vdim)))
+        return specs
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        n = self.names
+        self.qkv = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0).contiguous()
+        self.out_w = tensors[n["o"]].contiguous()
+        if self.qk_norm:
+            self.q_gain, self.k_gain = tensors[n["q_norm"]].contiguous(), tensors[n["k_norm"]].contiguous()
+
+    def forward(self, x: torch.Tensor, ctx, cache) -> torch.Tensor:
+        batch = ctx.batch
+        n = batch.num_tokens
+        table = batch.block_tables[cache.group]
+        qkv = ctx.buffer("sink_attn.qkv", (n, self.qkv_width))
+        linear(x, self.qkv, qkv, None, n, ctx)
+        kernels.head_norm_rope_write(qkv, self.q_gain, self.k_gain, self.eps, batch.positions, batch.seq_of_token, table,
+                                     cache.k_pages, cache.v_pages, n, self.heads, self.kv_heads, self.dim, self.vdim,
+                                     self.inv_freq, self.rot, self.interleaved, cache.writes, ctx.status)
+        attended = ctx.buffer("sink_attn.attended", (n, self.heads * self.vdim))
+        kernels.paged_attention_capped(qkv, attended, cache.k_pages, cache.v_pages, table, batch.seq_of_token, batch.positions,
+                                       n, self.heads, self.kv_heads, self.dim, self.vdim, self.window, self.scale,
+                                       self.softcap, self.sink, ctx.status)
+        out = ctx.buffer("sink_attn.out", (n, self.hidden_size))
+        linear(attended, self.out_w, out, None, n, ctx)
+        return out
+
+
+register_mixer("sink_attention", SinkAttention)

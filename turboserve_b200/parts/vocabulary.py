@@ -48,14 +48,16 @@ class LinearHead(LogitHead):
         self.hidden_size, self.vocab_size, self.tied = int(hidden_size), int(vocab_size), bool(tied)
         self.scale = float(spec.get("scale", 1.0))
         """The logits are multiplied by it (in float32, after the product)."""
+        self.tensor = str(spec.get("tensor", "weight"))
+        """The matrix's local name in the checkpoint."""
         self.weight: torch.Tensor | None = None
 
     def param_specs(self) -> list[ParamSpec]:
-        return [] if self.tied else [ParamSpec("weight", (self.vocab_size, self.hidden_size))]
+        return [] if self.tied else [ParamSpec(self.tensor, (self.vocab_size, self.hidden_size))]
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         if not self.tied:
-            self.weight = tensors["weight"].contiguous()
+            self.weight = tensors[self.tensor].contiguous()
 
     def tie(self, table: torch.Tensor) -> None:
         if tuple(table.shape) != (self.vocab_size, self.hidden_size):
