@@ -56,14 +56,18 @@ def sink_attention(h: torch.Tensor, w: dict, sizes: dict, eps: float) -> torch.T
     per = heads // kv_heads
     k, v = k.repeat_interleave(per, dim=1), v.repeat_interleave(per, dim=1)
     scores = torch.einsum("thd,shd->hts", q, k) * float(sizes["scale"])
-    cap = sizes.get("softcap")
+    positions = torch.arange(tokens)
+    weights = capped_sink_weights(scores, sizes.get("softcap"), positions[:, None] >= positions[None, :])
+    return torch.einsum("hts,shv->thv", weights, v).reshape(tokens, heads * vdim) @ w["o"].T
+
+
+def capped_sink_weights(scores: torch.Tensor, cap, seen: torch.Tensor) -> torch.Tensor:
+    """``p_j = exp(s_j) / (1 + sum_i exp(s_i))`` over the keys that are ``seen``, with ``s = cap tanh(score / cap)``
+    when there is a cap: the weights of a row add up to less than one, the rest is the sink's."""
     if cap:
         scores = float(cap) * torch.tanh(scores / float(cap))
-    positions = torch.arange(tokens)
-    seen = positions[:, None] >= positions[None, :]
     weights = torch.exp(scores).masked_fill(~seen, 0.0)
-    weights = weights / (1.0 + weights.sum(dim=-1, keepdim=True))
-    return torch.einsum("hts,shv->thv", weights, v).reshape(tokens, heads * vdim) @ w["o"].T
+    return weights / (1.0 + weights.sum(dim=-1, keepdim=True))
 
 
 def lightning_attention(h: torch.Tensor, w: dict, sizes: dict, eps: float) -> torch.Tensor:
