@@ -654,6 +654,26 @@ def filezen_raw(width: int, layers: int) -> dict:
             "norm": {"eps": 1e-6}, "initializer_range": 0.02, "layers": out}
 
 
+def begovik_raw(width: int, layers: int) -> dict:
+    """Begovik at the sizes of a real model's layers: side-by-side layers, the selective scan and wkv time mixing in turn
+    (p, m, w, m, ...). Side by side: attention with heads of 128 keys and values, four query heads to a key head, 64
+    rotated elements, scores capped at 50, a sink and no window, beside lightning attention with heads of 128 keys and
+    values (as wide as the model together). Selective scan: an inner width of twice the model's, a state of 16, step sizes
+    of rank width / 16, four taps. wkv: heads of 64, a decay pair of rank 64. Every layer has a clamped feed-forward of
+    4 x width."""
+    heads = max(4, width // 128)
+    left = dict(heads=heads, kv_heads=heads // 4, dim=128, vdim=128, scale=128 ** -0.5, softcap=50.0, rot={"base": 10000.0, "dims": 64})
+    r_heads = max(2, width // 128)
+    right = dict(heads=r_heads, dim=128, vdim=128, decay=[1.0 - 2.0 ** (-5 - i * 3 / r_heads) for i in range(r_heads)])
+    mlp = {"kind": "dense", "ff": 4 * width, "limit": 7.0}
+    side = {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp}
+    scan = {"type": "mamba1", "mixer": dict(inner=2 * width, state=16, dt_rank=width // 16, conv=4), "mlp": mlp}
+    wkv = {"type": "wkv", "mixer": dict(heads=width // 64, dim=64, decay_rank=64), "mlp": mlp}
+    pattern = [side, scan, wkv, scan]
+    return {"architecture": "Begovik", "vocab": DESIGN_VOCAB, "width": width, "embedding": {"scale": 1.0}, "residual_mult": 0.5,
+            "norm": {"eps": 1e-6}, "initializer_range": 0.02, "layers": [pattern[i % 4] for i in range(layers)]}
+
+
 class OpTimer:
     """CUDA events around every kernel entry point and matrix product a step calls, summed by name."""
 
@@ -679,15 +699,17 @@ class OpTimer:
 
     def __enter__(self) -> "OpTimer":
         from turboserve_b200.ops import kernels
-        from turboserve_b200.parts import attention, diff_attention, latent_attention, mamba2, mlp, moe, retention, vocabulary
+        from turboserve_b200.parts import (attention, diff_attention, latent_attention, mamba1, mamba2, mlp, moe, retention,
+                                           sink_attention, vocabulary, wkv)
 
         for name in ("embedding", "add_rmsnorm", "stream_norm", "act_mul", "activation", "rope_cache_write", "causal_conv",
                      "diff_attention", "diff_attention_mma", "ssd_scan", "gated_group_norm", "scale_rows", "norm_add",
                      "latent_prepare", "head_linear", "latent_attention", "latent_gather", "latent_softmax", "retention_scan",
-                     "head_norm_gate", "moe_route", "moe_pair_gate_up", "moe_pair_down", "moe_expert_rows", "moe_sort", "moe_gather", "moe_combine"):
+                     "head_norm_gate", "head_norm_rope_write", "paged_attention_capped", "sink_attention_mma", "norm_pair_mix",
+                     "shift_mix", "selective_scan", "chosen_decay_scan", "part_norm_gate", "moe_route", "moe_pair_gate_up", "moe_pair_down", "moe_expert_rows", "moe_sort", "moe_gather", "moe_combine"):
             if hasattr(kernels, name):
                 self._wrap(kernels, name, name)
-        for module in (attention, diff_attention, mamba2, mlp, vocabulary, latent_attention, retention):
+        for module in (attention, diff_attention, mamba2, mlp, vocabulary, latent_attention, retention, sink_attention, wkv, mamba1):
             self._wrap(module, "linear", "linear")
         self._wrap(moe, "linear", "expert_linear")
         self._wrap(latent_attention, "matrix_product", "latent_products")
@@ -741,13 +763,16 @@ def design_bench(size: str, steps: int, warmup: int, tokens: int = 2048, context
     peaks = load_peaks()
     of = "of measured" if peaks["source"] == "measured" else "of fallback"
     hbm, tensor = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
-    out = {"design": ("Filezen beside Baporax and Qwen2" if design == "filezen" else "Baporax beside Qwen2") + " at equal size",
+    titles = {"filezen": "Filezen beside Baporax and Qwen2", "begovik": "Begovik beside Baporax and Qwen2", "baporax": "Baporax beside Qwen2"}
+    out = {"design": titles[design] + " at equal size",
            "width": width, "layers": layers, "prompt_tokens": tokens,
            "decode_context": context, "window": DESIGN_WINDOW, "dtype": "bf16", "peaks": of, "models": {}}
     heads = max(4, width // 128)
     models = [("baporax", baporax_raw(width, layers)), ("qwen2", qwen2_equal_raw(width, layers))]
     if design == "filezen":
         models.insert(0, ("filezen", filezen_raw(width, layers)))
+    if design == "begovik":
+        models.insert(0, ("begovik", begovik_raw(width, layers)))
     if alone:
         models = [m for m in models if m[0] == design]
     for name, raw in models:
@@ -776,7 +801,38 @@ def design_bench(size: str, steps: int, warmup: int, tokens: int = 2048, context
         # the mixers' kernels against their rooflines (time of all layers of the kind in one step)
         kernels_out = {}
         seen = min(context, DESIGN_WINDOW)
-        if name == "filezen":
+        if name == "begovik":
+            # attention without a window: a prompt's rows see everything before them, a decoded token its whole context
+            side_layers = sum(1 for layer in raw["layers"] if layer["type"] == "parallel")
+            scan_layers = sum(1 for layer in raw["layers"] if layer["type"] == "mamba1")
+            wkv_layers = layers - side_layers - scan_layers
+            r_heads, w_heads, inner, n_state = max(2, width // 128), width // 64, 2 * width, 16
+            prefill = entry["prefill_ops_us"]
+            flops = side_layers * visible_pairs(tokens, None) * heads * 4 * 128
+            us = prefill.get("sink_attention_mma", 0.0) + prefill.get("paged_attention_capped", 0.0)
+            kernels_out["attention_prefill"] = {"us": us, "tflops": round(flops / us / 1e6, 1), "frac_tensor": round(flops / (us * 1e-6) / tensor, 4)}
+            scan_flops = side_layers * tokens * r_heads * 128 * 128 * 4
+            us = prefill.get("retention_scan", 0.0)
+            kernels_out["lightning_prefill"] = {"us": us, "fp32_tflops": round(scan_flops / us / 1e6, 2)}
+            scan_flops = wkv_layers * tokens * w_heads * 64 * 64 * 6
+            us = prefill.get("chosen_decay_scan", 0.0)
+            kernels_out["wkv_prefill"] = {"us": us, "fp32_tflops": round(scan_flops / us / 1e6, 2)}
+            scan_flops = scan_layers * tokens * inner * n_state * 6
+            scan_bytes = scan_layers * tokens * (inner * (2 + 4 + 2 + 2) + 2 * n_state * 2)
+            us = prefill.get("selective_scan", 0.0)
+            kernels_out["scan_prefill"] = {"us": us, "fp32_tflops": round(scan_flops / us / 1e6, 2), "frac_hbm": round(scan_bytes / (us * 1e-6) / hbm, 4)}
+            for batch in (8, 64):
+                ops = entry[f"decode_b{batch}_ops_us"]
+                bytes_read = side_layers * batch * context * (heads // 4) * 256 * 2
+                us = ops.get("paged_attention_capped", 0.0) + ops.get("sink_attention_mma", 0.0)
+                kernels_out[f"attention_decode_b{batch}"] = {"us": us, "gbs": round(bytes_read / us / 1e3, 1), "frac_hbm": round(bytes_read / (us * 1e-6) / hbm, 4)}
+                for label, key, state_bytes in (
+                        ("lightning", "retention_scan", side_layers * batch * r_heads * 128 * 128 * 4 * 2),
+                        ("wkv", "chosen_decay_scan", wkv_layers * batch * w_heads * 64 * 64 * 4 * 2),
+                        ("scan", "selective_scan", scan_layers * batch * inner * n_state * 4 * 2)):
+                    us = ops.get(key, 0.0)
+                    kernels_out[f"{label}_decode_b{batch}"] = {"us": us, "gbs": round(state_bytes / us / 1e3, 1), "frac_hbm": round(state_bytes / (us * 1e-6) / hbm, 4)}
+        elif name == "filezen":
             latent_layers = sum(1 for layer in raw["layers"] if layer["type"] == "latent_attention")
             owners = sum(1 for layer in raw["layers"] if layer["type"] == "latent_attention" and "kv_from" not in layer["mixer"])
             retention_layers = layers - latent_layers
@@ -858,7 +914,7 @@ def main() -> int:
     parser.add_argument("--sampling-sweep", action="store_true", help="time decode steps through LLMEngine under a few sets of sampling options and exit")
     parser.add_argument("--fp32-products", action="store_true", help="time the float32 path's matrix product at the 7B shapes and exit")
     parser.add_argument("--float32", action="store_true", help="with --one-step: the true 32-bit path")
-    parser.add_argument("--design", choices=["baporax", "filezen"], default=None,
+    parser.add_argument("--design", choices=["baporax", "filezen", "begovik"], default=None,
                         help="measure that design at real layer sizes beside Qwen2 at equal size and exit (see design_bench())")
     parser.add_argument("--design-size", choices=sorted(DESIGN_SIZES), default="2k", help="width and depth for --design")
     parser.add_argument("--design-alone", action="store_true", help="with --design: leave the models beside it out (profiling runs)")

@@ -92,10 +92,20 @@ CASES = {"A": (CASE_A, 41), "B": (CASE_B, 42), "C": (CASE_C, 43), "D": (CASE_D, 
 
 
 def write_case(name: str, folder: Path, sharp: bool = False) -> Path:
+    raw, seed = CASES[name]
+    return write_raw(raw, seed, folder, sharp)
+
+
+def one_layer(kind_and_mixer, mlp=None, width=64, vocab=90, scale=2.0, mult=0.8, eps=1e-5) -> dict:
+    """A model of one layer around one mixer (and no feed-forward unless given): a mechanism alone."""
+    return {"architecture": "Begovik", "vocab": vocab, "width": width, "embedding": {"scale": scale}, "residual_mult": mult,
+            "norm": {"eps": eps}, "layers": [layer(kind_and_mixer, mlp)]}
+
+
+def write_raw(raw: dict, seed: int, folder: Path, sharp: bool = False) -> Path:
     from turboserve_b200.config import config_from_dict
     from turboserve_b200.weights import write_random_model
 
-    raw, seed = CASES[name]
     if sharp:
         raw = json.loads(json.dumps(raw))
         for entry in raw["layers"]:
