@@ -705,7 +705,7 @@ class OpTimer:
         for name in ("embedding", "add_rmsnorm", "stream_norm", "act_mul", "activation", "rope_cache_write", "causal_conv",
                      "diff_attention", "diff_attention_mma", "ssd_scan", "gated_group_norm", "scale_rows", "norm_add",
                      "latent_prepare", "head_linear", "latent_attention", "latent_gather", "latent_softmax", "retention_scan",
-                     "head_norm_gate", "head_norm_rope_write", "paged_attention_capped", "sink_attention_mma", "norm_pair_mix",
+                     "head_norm_gate", "head_norm_rope_write", "paged_attention_capped", "paged_attention_capped_mma", "norm_pair_mix",
                      "shift_mix", "selective_scan", "chosen_decay_scan", "part_norm_gate", "moe_route", "moe_pair_gate_up", "moe_pair_down", "moe_expert_rows", "moe_sort", "moe_gather", "moe_combine"):
             if hasattr(kernels, name):
                 self._wrap(kernels, name, name)
@@ -809,7 +809,7 @@ def design_bench(size: str, steps: int, warmup: int, tokens: int = 2048, context
             r_heads, w_heads, inner, n_state = max(2, width // 128), width // 64, 2 * width, 16
             prefill = entry["prefill_ops_us"]
             flops = side_layers * visible_pairs(tokens, None) * heads * 4 * 128
-            us = prefill.get("sink_attention_mma", 0.0) + prefill.get("paged_attention_capped", 0.0)
+            us = prefill.get("paged_attention_capped_mma", 0.0) + prefill.get("paged_attention_capped", 0.0)
             kernels_out["attention_prefill"] = {"us": us, "tflops": round(flops / us / 1e6, 1), "frac_tensor": round(flops / (us * 1e-6) / tensor, 4)}
             scan_flops = side_layers * tokens * r_heads * 128 * 128 * 4
             us = prefill.get("retention_scan", 0.0)
@@ -824,7 +824,7 @@ def design_bench(size: str, steps: int, warmup: int, tokens: int = 2048, context
             for batch in (8, 64):
                 ops = entry[f"decode_b{batch}_ops_us"]
                 bytes_read = side_layers * batch * context * (heads // 4) * 256 * 2
-                us = ops.get("paged_attention_capped", 0.0) + ops.get("sink_attention_mma", 0.0)
+                us = ops.get("paged_attention_capped", 0.0) + ops.get("paged_attention_capped_mma", 0.0)
                 kernels_out[f"attention_decode_b{batch}"] = {"us": us, "gbs": round(bytes_read / us / 1e3, 1), "frac_hbm": round(bytes_read / (us * 1e-6) / hbm, 4)}
                 for label, key, state_bytes in (
                         ("lightning", "retention_scan", side_layers * batch * r_heads * 128 * 128 * 4 * 2),

@@ -160,10 +160,19 @@ def relative_error(ours: torch.Tensor, ref: torch.Tensor) -> torch.Tensor:
     return diff.pow(2).mean(-1).sqrt() / centred.pow(2).mean().sqrt()
 
 
-def check(ours: torch.Tensor, ref: torch.Tensor, dtype: str, what: str, slack: float = 1.0) -> None:
+JITTER = 2.0 ** -8
+"""Relative noise on every sublayer's input and output in the plain implementation's shaken run (bfloat16 has 8 bits)."""
+
+
+def check(ours: torch.Tensor, ref: torch.Tensor, dtype: str, what: str, slack: float = 1.0, shaken: torch.Tensor | None = None) -> None:
+    """``shaken``: the plain logits under relative noise of ``JITTER``. Where they move far a position is touchy by the
+    design itself (a head's output of nearly no length brought to unit length, say) and gets that much more room."""
     assert ours.shape == ref.shape, f"{what}: shape {tuple(ours.shape)} vs {tuple(ref.shape)}"
     assert torch.isfinite(ours).all(), f"{what}: non-finite logits"
     error = relative_error(ours, ref)
-    bound = (FP32_REL if dtype == "float32" else BF16_REL) * slack
-    worst = float(error.max())
-    assert worst <= bound, f"{what}: relative error {worst:.3e} at position {int(error.argmax())} (bound {bound:.1e})"
+    bound = torch.full_like(error, (FP32_REL if dtype == "float32" else BF16_REL) * slack)
+    if shaken is not None:
+        bound = bound + 3.0 * relative_error(shaken, ref)
+    over = error - bound
+    worst = int(over.argmax())
+    assert float(over.max()) <= 0.0, f"{what}: relative error {float(error[worst]):.3e} at position {worst} (bound {float(bound[worst]):.1e})"

@@ -157,18 +157,27 @@ def part(weights: dict, prefix: str) -> dict:
     return {name[len(prefix):]: t.to(F64) for name, t in weights.items() if name.startswith(prefix)}
 
 
-def forward(config: dict, weights: dict, tokens: list[int]) -> tuple[torch.Tensor, torch.Tensor]:
-    """Logits [T, vocab] and the stream after every layer [layers, T, width]."""
+def forward(config: dict, weights: dict, tokens: list[int], jitter: float = 0.0) -> tuple[torch.Tensor, torch.Tensor]:
+    """Logits [T, vocab] and the stream after every layer [layers, T, width].
+
+    ``jitter``: every sublayer's input and output is multiplied by ``1 + jitter * noise`` (unit normal noise per
+    element): how far a position's logits move under relative errors of that size, as rounding to a short
+    mantissa makes them."""
     eps, mult = float(config["norm"]["eps"]), float(config["residual_mult"])
+    noise = torch.Generator().manual_seed(7)
+
+    def shaken(t: torch.Tensor) -> torch.Tensor:
+        return t * (1.0 + jitter * torch.randn(t.shape, generator=noise, dtype=F64)) if jitter else t
+
     x = weights["embed"].to(F64)[torch.tensor(tokens)] * float(config["embedding"]["scale"])
     after = []
     for index, layer in enumerate(config["layers"]):
         name = f"l{index}."
-        update = MIXERS[layer["type"]](rms_norm(x, weights[name + "norm1"].to(F64), eps), part(weights, name + "mix."),
-                                       layer["mixer"], eps)
+        update = shaken(MIXERS[layer["type"]](shaken(rms_norm(x, weights[name + "norm1"].to(F64), eps)), part(weights, name + "mix."),
+                                              layer["mixer"], eps))
         if layer.get("mlp"):
-            update = update + clamped_feed_forward(rms_norm(x, weights[name + "norm2"].to(F64), eps),
-                                                   part(weights, name + "mlp."), layer["mlp"])
+            update = update + shaken(clamped_feed_forward(shaken(rms_norm(x, weights[name + "norm2"].to(F64), eps)),
+                                                          part(weights, name + "mlp."), layer["mlp"]))
         x = x + mult * update
         after.append(x)
     final = rms_norm(x, weights["final.norm"].to(F64), eps)

@@ -41,13 +41,13 @@ def folders(tmp_path_factory):
     return _folders
 
 
-def reference(folder, requests):
+def reference(folder, requests, jitter=0.0):
     config, weights = P.read_model_folder(folder)
     out = {}
     for rid, tokens in requests.items():
-        key = (str(folder), tuple(tokens))
+        key = (str(folder), tuple(tokens), jitter)
         if key not in _references:
-            _references[key] = P.logits_of(config, weights, tokens)
+            _references[key] = P.forward(config, weights, tokens, jitter)[0]
         out[rid] = _references[key]
     return out
 
@@ -61,8 +61,9 @@ def run_and_check(folder, dtype, builder, lengths, page_size=16, slack=1.0, **kw
     replayer = Replayer(folder, dtype, max_tokens, page_size=page_size)
     got = traces.collect(requests, steps, traces.replay(replayer, steps))
     ref = reference(folder, requests)
+    shaken = reference(folder, requests, C.JITTER) if dtype == "bfloat16" else None
     for rid in requests:
-        C.check(got[rid], ref[rid], dtype, f"{dtype} {builder.__name__} {rid}", slack)
+        C.check(got[rid], ref[rid], dtype, f"{dtype} {builder.__name__} {rid}", slack, shaken[rid] if shaken else None)
     replayer.manager.check_invariants()
     assert replayer.manager.free_pages() == [g.num_pages for g in replayer.manager.groups]
     return replayer, got
@@ -102,13 +103,14 @@ def test_attention_with_a_cap_and_a_sink(dtype, heads, kv_heads, dim, vdim, cap,
     v = torch.randn(tokens, kv_heads, vdim, generator=g)
     per = heads // kv_heads
     marks = {299: 7, 298: 0, 297: 299 - page_size, 296: 299 - page_size + 1, 295: 295 - 255, 250: 250, 200: 3}
+    common = torch.randn(dim, generator=g)
+    common = common / common.norm()
     for query, key in marks.items():  # query `query` looks for key `key` with every head
         direction = torch.randn(dim, generator=g)
+        direction = direction - (direction @ common) * common  # (the marked keys stay as unloved as the others below)
         direction = direction / direction.norm()
         k[key] = k[key] + 6.0 * direction
         q[query] = q[query] + 6.0 * direction
-    common = torch.randn(dim, generator=g)
-    common = common / common.norm()
     k = k + 2.0 * common
     q[100:120] = q[100:120] - 14.0 * common  # rows that like nothing they see
     q, k, v = q.to(dtype), k.to(dtype), v.to(dtype)
@@ -144,6 +146,27 @@ def test_attention_with_a_cap_and_a_sink(dtype, heads, kv_heads, dim, vdim, cap,
         assert torch.equal(tail, whole[290:])  # one order of every sum, alone or in a portion
     portion = run(180, 120)
     assert (portion - want[180:]).abs().max() <= tol * max(1.0, float(want.abs().max()))
+    if not kernels.paged_attention_capped_mma_takes(dtype, dim, vdim, scale):
+        return
+
+    # the tiled kernel: a whole prompt; then the end of the same request beside another request's first portion
+    def tiled(parts):
+        rows = torch.cat([q[first:first + count] for first, count in parts]).reshape(-1, heads * dim).cuda()
+        starts = [0]
+        for _, count in parts:
+            starts.append(starts[-1] + count)
+        out = torch.zeros(starts[-1], heads * vdim + 8, dtype=dtype, device="cuda")
+        kernels.paged_attention_capped_mma(rows, out, k_pages, v_pages, _i32([order] * len(parts)), _i32(starts),
+                                           _i32([first + count for first, count in parts]), starts[-1], len(parts), heads,
+                                           kv_heads, dim, vdim, None, scale, cap, sink)
+        return out[:, :heads * vdim].cpu().double()
+
+    bound = 2e-2 * max(1.0, float(want.abs().max()))
+    assert (tiled([(0, tokens)]) - want).abs().max() <= bound
+    both = tiled([(180, 120), (0, 70)])
+    assert (both[:120] - want[180:]).abs().max() <= bound and (both[120:] - want[:70]).abs().max() <= bound
+    assert torch.equal(tiled([(0, tokens)])[180:], both[:120])  # the same bits however the request is cut
+    assert torch.equal(tiled([(299, 1)]), both[119:120])
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

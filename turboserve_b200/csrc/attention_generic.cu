@@ -147,6 +147,219 @@ paged_attention_generic_kernel(const T* __restrict__ q, long long q_stride, T* _
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same, one block per (query token, key head): the QH query heads that share a key head are
+// scored against every key row and accumulate every value row together, so a step that decodes
+// reads its keys and values once, 16 bytes at a time where the rows are 16-byte aligned.  Sixteen
+// warps, one per stream; a tile's weights go through a small buffer in shared memory from the lanes
+// that scored the keys to all lanes for the value sum.  Streams are merged by one warp per head.
+// Every sum has the order of the kernel above, so both give the same bits.
+// ---------------------------------------------------------------------------------------------
+#define GROUP_MAX_PER_LANE 4  // v_dim <= 128
+
+template <typename T> struct RowVec;
+template <> struct RowVec<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+    const float4 x = *reinterpret_cast<const float4*>(p);
+    v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+  }
+};
+template <> struct RowVec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 x = *reinterpret_cast<const uint4*>(p);
+    const unsigned w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+};
+
+template <typename T, int QH>
+__global__ void __launch_bounds__(GENERIC_STREAMS * 32)
+paged_attention_group_kernel(const T* __restrict__ q, long long q_stride, T* __restrict__ out, long long out_stride,
+                             const T* __restrict__ k_pages, const T* __restrict__ v_pages,
+                             const int* __restrict__ block_table, int table_stride, const int* __restrict__ seq_of_token,
+                             const int* __restrict__ positions, int page_size, int num_kv_heads, int head_dim, int v_dim,
+                             int window, float scale, float softcap, int sink, int vector_rows, int* __restrict__ status) {
+  pdl_wait();
+  pdl_trigger();
+  extern __shared__ __align__(16) float smem[];
+  float* q_s = smem;                                               // [QH][head_dim]
+  float* part_acc = q_s + QH * head_dim;                           // [GENERIC_STREAMS][QH][v_dim]
+  float* part_ml = part_acc + GENERIC_STREAMS * QH * v_dim;        // [GENERIC_STREAMS][QH][2]
+  float* weights = part_ml + GENERIC_STREAMS * QH * 2;             // [GENERIC_STREAMS][32][QH]
+  unsigned long long* rows_s = reinterpret_cast<unsigned long long*>(weights + GENERIC_STREAMS * 32 * QH);  // [GENERIC_STREAMS][32]
+
+  const int t = blockIdx.x, kv_head = blockIdx.y;
+  const int seq = seq_of_token[t];
+  if (seq < 0) return;
+  const int pos = positions[t];
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int* table = block_table + (size_t)seq * table_stride;
+  const T* q_row = q + (size_t)t * q_stride + (size_t)kv_head * QH * head_dim;
+  for (int i = threadIdx.x; i < QH * head_dim; i += blockDim.x) q_s[i] = to_float(q_row[i]);
+  __syncthreads();
+
+  const int num_tiles = (pos - lo + 32) / 32;
+  const int stream = warp;
+  float* my_weights = weights + stream * 32 * QH;
+  unsigned long long* my_rows = rows_s + stream * 32;
+  float top[QH], sum[QH];
+  float acc[QH][GROUP_MAX_PER_LANE];
+#pragma unroll
+  for (int h = 0; h < QH; ++h) {
+    top[h] = -INFINITY;
+    sum[h] = 0.0f;
+#pragma unroll
+    for (int i = 0; i < GROUP_MAX_PER_LANE; ++i) acc[h][i] = 0.0f;
+  }
+  for (int tile = stream; tile < num_tiles; tile += GENERIC_STREAMS) {
+    const int key = lo + tile * 32 + lane;
+    float d[QH];
+#pragma unroll
+    for (int h = 0; h < QH; ++h) d[h] = 0.0f;
+    bool readable = false;
+    size_t v_row = 0;
+    if (key <= pos) {
+      const int page = table[key / page_size];
+      if (page < 0) {
+        if (status) atomicOr(status, 4);
+      } else {
+        readable = true;
+        const size_t place = ((size_t)page * page_size + key % page_size) * num_kv_heads + kv_head;
+        v_row = place * v_dim;
+        const T* k_row = k_pages + place * head_dim;
+        if (vector_rows) {
+          constexpr int W = RowVec<T>::N;
+#pragma unroll 4
+          for (int i = 0; i < head_dim; i += W) {
+            float kv[W];
+            RowVec<T>::load(k_row + i, kv);
+#pragma unroll
+            for (int h = 0; h < QH; ++h) {
+              const float* qh = q_s + h * head_dim + i;
+              float total = d[h];
+#pragma unroll
+              for (int e = 0; e < W; ++e) total = fmaf(qh[e], kv[e], total);
+              d[h] = total;
+            }
+          }
+        } else {
+          for (int i = 0; i < head_dim; ++i) {
+            const float kv = to_float(k_row[i]);
+#pragma unroll
+            for (int h = 0; h < QH; ++h) d[h] = fmaf(q_s[h * head_dim + i], kv, d[h]);
+          }
+        }
+      }
+    }
+    bool any = false;
+#pragma unroll
+    for (int h = 0; h < QH; ++h) {
+      float sc = -INFINITY;
+      if (readable) {
+        sc = d[h] * scale;
+        if (softcap > 0.0f) sc = softcap * tanhf(sc / softcap);
+      }
+      const float next = fmaxf(top[h], warp_max(sc));
+      float p = 0.0f, corr = 1.0f;
+      if (next != -INFINITY) {
+        any = true;
+        corr = expf(top[h] - next);
+        p = sc == -INFINITY ? 0.0f : expf(sc - next);
+        sum[h] = sum[h] * corr + warp_sum(p);
+        top[h] = next;
+      }
+#pragma unroll
+      for (int i = 0; i < GROUP_MAX_PER_LANE; ++i) acc[h][i] *= corr;
+      my_weights[lane * QH + h] = p;
+    }
+    my_rows[lane] = (unsigned long long)v_row;
+    __syncwarp();
+    if (any) {
+      const int in_tile = min(32, pos - (lo + tile * 32) + 1);
+#pragma unroll 4
+      for (int j = 0; j < in_tile; ++j) {
+        const T* v = v_pages + my_rows[j];
+        float x[GROUP_MAX_PER_LANE];
+#pragma unroll
+        for (int i = 0; i < GROUP_MAX_PER_LANE; ++i) {
+          const int e = lane + 32 * i;
+          x[i] = e < v_dim ? to_float(v[e]) : 0.0f;
+        }
+        const float* w = my_weights + j * QH;
+#pragma unroll
+        for (int h = 0; h < QH; ++h) {
+          const float wh = w[h];
+#pragma unroll
+          for (int i = 0; i < GROUP_MAX_PER_LANE; ++i) acc[h][i] = fmaf(wh, x[i], acc[h][i]);
+        }
+      }
+    }
+    __syncwarp();
+  }
+#pragma unroll
+  for (int h = 0; h < QH; ++h) {
+#pragma unroll
+    for (int i = 0; i < GROUP_MAX_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (e < v_dim) part_acc[(stream * QH + h) * v_dim + e] = acc[h][i];
+    }
+    if (lane == 0) {
+      part_ml[(stream * QH + h) * 2] = top[h];
+      part_ml[(stream * QH + h) * 2 + 1] = sum[h];
+    }
+  }
+  __syncthreads();
+  if (warp < QH) {
+    const int h = warp;
+    float m_all = -INFINITY;
+    for (int w = 0; w < GENERIC_STREAMS; ++w) m_all = fmaxf(m_all, part_ml[(w * QH + h) * 2]);
+    float weight[GENERIC_STREAMS];
+    float l_all = 0.0f;
+    if (sink) {
+      m_all = fmaxf(m_all, 0.0f);
+      l_all = expf(-m_all);
+    }
+    for (int w = 0; w < GENERIC_STREAMS; ++w) {
+      const float mw = part_ml[(w * QH + h) * 2];
+      weight[w] = mw == -INFINITY ? 0.0f : expf(mw - m_all);
+      l_all += part_ml[(w * QH + h) * 2 + 1] * weight[w];
+    }
+    const float inv = l_all > 0.0f ? 1.0f / l_all : 0.0f;
+    T* o_row = out + (size_t)t * out_stride + (size_t)(kv_head * QH + h) * v_dim;
+    for (int dim = lane; dim < v_dim; dim += 32) {
+      float v = 0.0f;
+      for (int w = 0; w < GENERIC_STREAMS; ++w) v += part_acc[(w * QH + h) * v_dim + dim] * weight[w];
+      o_row[dim] = from_float<T>(v * inv);
+    }
+  }
+}
+
+template <typename T, int QH>
+static int paged_attention_group_launch(const void* q, long long q_stride, void* out, long long out_stride,
+                                        const void* k_pages, const void* v_pages, const int* block_table,
+                                        int table_stride, const int* seq_of_token, const int* positions, int num_tokens,
+                                        int page_size, int num_kv_heads, int head_dim, int v_dim, int window, float scale,
+                                        float softcap, int sink, int* status, cudaStream_t stream) {
+  const size_t floats = (size_t)QH * head_dim + (size_t)GENERIC_STREAMS * QH * v_dim + (size_t)GENERIC_STREAMS * QH * 2 +
+                        (size_t)GENERIC_STREAMS * 32 * QH;
+  const size_t smem = floats * sizeof(float) + (size_t)GENERIC_STREAMS * 32 * sizeof(unsigned long long);
+  if (smem > 200 * 1024) return TS_ERR_SIZE;
+  auto kernel = paged_attention_group_kernel<T, QH>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const int vector_rows = (head_dim * sizeof(T)) % 16 == 0 && !((uintptr_t)k_pages & 15);
+  ts_launch(kernel, dim3(num_tokens, num_kv_heads), dim3(GENERIC_STREAMS * 32), smem, stream, (const T*)q, q_stride, (T*)out,
+            out_stride, (const T*)k_pages, (const T*)v_pages, block_table, table_stride, seq_of_token, positions, page_size,
+            num_kv_heads, head_dim, v_dim, window, scale, softcap, sink, vector_rows, status);
+  return ts_launch_status();
+}
+
 // The kernel with every option: value rows of their own width (v_dim), scores capped as
 // softcap * tanh(score / softcap) (softcap 0: as they are), and a sink (sink != 0: the softmax's
 // denominator is one larger, as if one more key scored 0 and had no value).
@@ -161,6 +374,26 @@ TS_EXPORT int ts_paged_attention_capped(int dtype, const void* q, long long q_st
   if (head_dim < 1 || head_dim > 32 * MAX_DIMS_PER_LANE || v_dim < 1 || v_dim > 32 * MAX_DIMS_PER_LANE) return TS_ERR_SIZE;
   if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads) return TS_ERR_SIZE;
   if (num_heads > 65535 || page_size < 1 || window < 0 || softcap < 0.0f) return TS_ERR_ARGUMENT;
+  const int per_group = num_heads / num_kv_heads;
+  // a step of few tokens (decoding): the heads of a key head together, keys and values read once
+  if ((long long)num_tokens * num_heads <= 2048 && per_group <= 8 && v_dim <= 32 * GROUP_MAX_PER_LANE && num_kv_heads <= 65535 &&
+      (dtype == TS_F32 || dtype == TS_BF16)) {
+#define GROUP_CASE(HEADS)                                                                                               \
+  case HEADS:                                                                                                           \
+    return dtype == TS_F32                                                                                              \
+               ? paged_attention_group_launch<float, HEADS>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, \
+                                                            table_stride, seq_of_token, positions, num_tokens, page_size, \
+                                                            num_kv_heads, head_dim, v_dim, window, scale, softcap, sink, \
+                                                            status, stream)                                              \
+               : paged_attention_group_launch<__nv_bfloat16, HEADS>(q, q_stride, out, out_stride, k_pages, v_pages,     \
+                                                                    block_table, table_stride, seq_of_token, positions, \
+                                                                    num_tokens, page_size, num_kv_heads, head_dim, v_dim, \
+                                                                    window, scale, softcap, sink, status, stream)
+    switch (per_group) {
+      GROUP_CASE(1); GROUP_CASE(2); GROUP_CASE(3); GROUP_CASE(4); GROUP_CASE(5); GROUP_CASE(6); GROUP_CASE(7); GROUP_CASE(8);
+    }
+#undef GROUP_CASE
+  }
   dim3 grid(num_tokens, num_heads);
   const size_t smem = ((size_t)head_dim + (size_t)v_dim * GENERIC_STREAMS + 2 * GENERIC_STREAMS) * sizeof(float);
   // few blocks (a decode step): a warp per stream; many: four warps, four streams each

@@ -34,6 +34,7 @@ BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC
 LIBRARIES: dict[str, tuple[str, tuple[str, ...]]] = {
     "layer_ops": ("layer_ops.cu", ()),
     "attention_generic": ("attention_generic.cu", ()),
+    "attention_capped_mma": ("attention_capped_mma.cu", ()),
     "attention_bf16": ("attention_bf16.cu", ()),
     "attention_tc": ("attention_tc.cu", ()),
     "gemm_simt": ("gemm_simt.cu", ()),

@@ -283,6 +283,38 @@ def paged_attention_capped(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Te
               1 if sink else 0, _ptr(status), _stream()), "paged_attention_capped")
 
 
+def paged_attention_capped_mma_takes(dtype: torch.dtype, dim: int, vdim: int, scale: float = 1.0) -> bool:
+    """Whether the tensor-core kernel for portions of prompts takes these sizes (else the kernel for every size runs)."""
+    return (dtype == torch.bfloat16 and dim % 16 == 0 and vdim % 16 == 0 and 16 <= dim <= 256 and 16 <= vdim <= 128
+            and scale > 0.0)
+
+
+def paged_attention_capped_mma(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                               block_table: torch.Tensor, query_start: torch.Tensor, context_lens: torch.Tensor,
+                               num_tokens: int, num_seqs: int, num_heads: int, num_kv_heads: int, head_dim: int, v_dim: int,
+                               window: int | None, scale: float, softcap: float = 0.0, sink: bool = False,
+                               status: torch.Tensor | None = None) -> None:
+    """:func:`paged_attention_capped` for bfloat16 steps with portions of prompts, on tensor cores: tiles of 64
+    positions of a request, found through ``query_start`` and ``context_lens`` (``[seqs + 1]`` and ``[seqs]``)."""
+    for name, tensor in (("q", q), ("out", out), ("k_pages", k_pages), ("v_pages", v_pages)):
+        _need(tensor, torch.bfloat16, name)
+    _need(block_table, torch.int32, "block_table"); _need(query_start, torch.int32, "query_start"); _need(context_lens, torch.int32, "context_lens")
+    if (not k_pages.is_contiguous() or not v_pages.is_contiguous() or tuple(k_pages.shape[2:]) != (num_kv_heads, head_dim)
+            or tuple(v_pages.shape[2:]) != (num_kv_heads, v_dim) or k_pages.shape[1] != v_pages.shape[1]):
+        raise KernelError("paged_attention_capped_mma: pages must be contiguous [pages, page_size, kv_heads, head_dim | v_dim]")
+    if q.shape[1] < num_heads * head_dim or out.shape[1] < num_heads * v_dim:
+        raise KernelError("paged_attention_capped_mma: q or out is narrower than its heads")
+    if query_start.numel() < num_seqs + 1 or context_lens.numel() < num_seqs:
+        raise KernelError("paged_attention_capped_mma: fewer requests than asked for")
+    fn = _fn("attention_capped_mma", "ts_paged_attention_capped_mma",
+             [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
+              block_table.stride(0), _ptr(query_start), _ptr(context_lens), num_tokens, num_seqs, k_pages.shape[1],
+              num_heads, num_kv_heads, head_dim, v_dim, int(window or 0), float(scale), float(softcap), 1 if sink else 0,
+              _ptr(status), _stream()), "paged_attention_capped_mma")
+
+
 # ---------------------------------------------------------------------------------------
 # stream_ops.cu
 # ---------------------------------------------------------------------------------------

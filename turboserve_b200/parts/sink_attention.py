@@ -14,7 +14,10 @@ biases; query head ``j`` reads key/value head ``j // (heads / kv_heads)``. Optio
 * ``window``: the keys seen, the query's own included (``None``: all up to its position).
 
 Norm, rotation and the append of keys and values to the request's pages are one kernel in fp32; scores, the
-softmax and its sums are fp32 in the attention kernel. ``names`` maps the roles ``q k v o q_norm k_norm`` to the
+softmax and its sums are fp32 in the attention kernel. bfloat16 steps with portions of prompts run the tiled
+tensor-core kernel (``attention_capped_mma.cu``) when it takes the head sizes; steps of single tokens, float32 and
+other sizes the kernel for every size (``attention_generic.cu``), which scores the query heads of a key head together
+when a step has few tokens. ``names`` maps the roles ``q k v o q_norm k_norm`` to the
 checkpoint's local tensor names.
 """
 
@@ -102,9 +105,15 @@ class SinkAttention(Mixer):
                                      cache.k_pages, cache.v_pages, n, self.heads, self.kv_heads, self.dim, self.vdim,
                                      self.inv_freq, self.rot, self.interleaved, cache.writes, ctx.status)
         attended = ctx.buffer("sink_attn.attended", (n, self.heads * self.vdim))
-        kernels.paged_attention_capped(qkv, attended, cache.k_pages, cache.v_pages, table, batch.seq_of_token, batch.positions,
-                                       n, self.heads, self.kv_heads, self.dim, self.vdim, self.window, self.scale,
-                                       self.softcap, self.sink, ctx.status)
+        if batch.max_query_len > 1 and kernels.paged_attention_capped_mma_takes(qkv.dtype, self.dim, self.vdim, self.scale):
+            # portions of prompts in bfloat16: tiles of 64 positions on tensor cores
+            kernels.paged_attention_capped_mma(qkv, attended, cache.k_pages, cache.v_pages, table, batch.query_start_loc,
+                                               batch.context_lens, n, batch.num_seqs, self.heads, self.kv_heads, self.dim,
+                                               self.vdim, self.window, self.scale, self.softcap, self.sink, ctx.status)
+        else:
+            kernels.paged_attention_capped(qkv, attended, cache.k_pages, cache.v_pages, table, batch.seq_of_token, batch.positions,
+                                           n, self.heads, self.kv_heads, self.dim, self.vdim, self.window, self.scale,
+                                           self.softcap, self.sink, ctx.status)
         out = ctx.buffer("sink_attn.out", (n, self.hidden_size))
         linear(attended, self.out_w, out, None, n, ctx)
         return out
