@@ -365,11 +365,17 @@ TS_EXPORT int ts_gated_group_norm(int dtype, const float* y, const void* z, long
 // request lives in its slot ([slots][inner][N], fp32), is read once before the step's first position of the
 // request and written once after its last.  A block owns one request and SEL_THREADS / L channels; L lanes share a
 // channel, lane l holding states l, l + L, ... in registers (at most SEL_PER_LANE of them), and add their parts of
-// y by shuffles in a fixed order.  Positions come SEL_BATCH at a time through shared memory.  One token per request
-// and long portions run the same code, so an output is the same bits however a request is cut into steps.
+// y by shuffles in a fixed order.  Positions come `batch` at a time through shared memory (as many as fit, up to
+// SEL_BATCH).  L follows from `inner` and N alone: the fewest lanes that leave a lane SEL_PER_LANE states, then doubled
+// while the grid of one request has fewer than SEL_BLOCKS blocks, so that one long portion fills the SMs; a block is a
+// warp group with little shared memory, so several are resident per SM and one's loads hide behind another's
+// arithmetic.  One token per request and long portions run the same code, so an output is the same bits however a
+// request is cut into steps.
 // ---------------------------------------------------------------------------------------
 #define SEL_THREADS 128
-#define SEL_BATCH 8
+#define SEL_BATCH 32
+#define SEL_BLOCKS 296  // two blocks for each of 148 SMs
+#define SEL_SMEM (40 * 1024)
 #define SEL_PER_LANE 16
 
 template <typename T, int NPL>  // NPL: states a lane (1, 2, 4, 8 or 16)
@@ -379,15 +385,16 @@ selective_scan_kernel(const T* __restrict__ x, long long x_stride, const float* 
                       int c_first, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                       const T* __restrict__ z, long long z_stride, float* __restrict__ state, T* __restrict__ out,
                       long long out_stride, const int* __restrict__ query_start, const int* __restrict__ slots, int inner,
-                      int n_state, int lanes) {
+                      int n_state, int lanes, int batch) {
   extern __shared__ __align__(16) float sel_smem[];
   const int channels = SEL_THREADS / lanes;              // channels a block
   const int npad = lanes * NPL;                          // states, padded
-  float* x_s = sel_smem;                                 // [SEL_BATCH][channels]
-  float* dt_s = x_s + SEL_BATCH * channels;              // [SEL_BATCH][channels]
-  float* z_s = dt_s + SEL_BATCH * channels;              // [SEL_BATCH][channels]
-  float* b_s = z_s + SEL_BATCH * channels;               // [SEL_BATCH][npad]
-  float* c_s = b_s + SEL_BATCH * npad;                   // [SEL_BATCH][npad]
+  float* x_s = sel_smem;                                 // [batch][channels]
+  float* dt_s = x_s + batch * channels;                  // [batch][channels]
+  float* z_s = dt_s + batch * channels;                  // [batch][channels]
+  float* y_s = z_s + batch * channels;                   // [batch][channels]
+  float* b_s = y_s + batch * channels;                   // [batch][npad]
+  float* c_s = b_s + batch * npad;                       // [batch][npad]
   const int seq = blockIdx.x, tid = threadIdx.x;
   const int dl = tid % lanes, cl = tid / lanes, ch = blockIdx.y * channels + cl;
   const bool live = ch < inner;
@@ -397,7 +404,6 @@ selective_scan_kernel(const T* __restrict__ x, long long x_stride, const float* 
     const int n = dl + i * lanes;
     a[i] = (live && n < n_state) ? -expf(a_log[(size_t)ch * n_state + n]) : 0.0f;
   }
-  const float bias = live ? dt_bias[ch] : 0.0f, skip = live ? d_skip[ch] : 0.0f;
   pdl_wait();
   pdl_trigger();
   const int first = query_start[seq], last = query_start[seq + 1];
@@ -408,9 +414,10 @@ selective_scan_kernel(const T* __restrict__ x, long long x_stride, const float* 
     const int n = dl + i * lanes;
     s[i] = (live && n < n_state) ? s_ptr[n] : 0.0f;
   }
-  for (int t0 = first; t0 < last; t0 += SEL_BATCH) {
-    const int count = min(SEL_BATCH, last - t0);
+  for (int t0 = first; t0 < last; t0 += batch) {
+    const int count = min(batch, last - t0);
     __syncthreads();  // everyone is done with the batch before
+#pragma unroll 4
     for (int idx = tid; idx < count * channels; idx += SEL_THREADS) {
       const int p = idx / channels, c = blockIdx.y * channels + idx % channels;
       float xv = 0.0f, dv = 0.0f, zv = 0.0f;
@@ -424,6 +431,7 @@ selective_scan_kernel(const T* __restrict__ x, long long x_stride, const float* 
       dt_s[idx] = dv;
       z_s[idx] = zv;
     }
+#pragma unroll 4
     for (int idx = tid; idx < count * npad; idx += SEL_THREADS) {
       const int p = idx / npad, n = idx % npad;
       const T* row = bc + (size_t)(t0 + p) * bc_stride;
@@ -431,9 +439,10 @@ selective_scan_kernel(const T* __restrict__ x, long long x_stride, const float* 
       c_s[idx] = n < n_state ? to_float(row[c_first + n]) : 0.0f;
     }
     __syncthreads();
+#pragma unroll 4
     for (int p = 0; p < count; ++p) {
-      const float xv = x_s[p * channels + cl], dt = dt_s[p * channels + cl];
-      const float dx = dt * xv;
+      const float dt = dt_s[p * channels + cl];
+      const float dx = dt * x_s[p * channels + cl];
       const float* bp = b_s + p * npad + dl;
       const float* cp = c_s + p * npad + dl;
       float y = 0.0f;
@@ -443,9 +452,15 @@ selective_scan_kernel(const T* __restrict__ x, long long x_stride, const float* 
         y = fmaf(s[i], cp[i * lanes], y);
       }
       for (int offset = lanes >> 1; offset > 0; offset >>= 1) y += __shfl_xor_sync(0xffffffffu, y, offset);
-      if (dl == 0 && live) {
-        const float zv = z_s[p * channels + cl];
-        out[(size_t)(t0 + p) * out_stride + ch] = from_float<T>(fmaf(skip, xv, y) * (zv / (1.0f + expf(-zv))));
+      if (dl == 0) y_s[p * channels + cl] = y;
+    }
+    __syncthreads();
+    // the skip, the gate and the store, once per output and along the channels
+    for (int idx = tid; idx < count * channels; idx += SEL_THREADS) {
+      const int p = idx / channels, c = blockIdx.y * channels + idx % channels;
+      if (c < inner) {
+        const float zv = z_s[idx];
+        out[(size_t)(t0 + p) * out_stride + c] = from_float<T>(fmaf(d_skip[c], x_s[idx], y_s[idx]) * (zv / (1.0f + expf(-zv))));
       }
     }
   }
@@ -456,7 +471,6 @@ selective_scan_kernel(const T* __restrict__ x, long long x_stride, const float* 
       if (n < n_state) s_ptr[n] = s[i];
     }
   }
-  (void)bias;
 }
 
 template <typename T>
@@ -469,16 +483,20 @@ static int launch_selective_scan(const T* x, long long x_stride, const float* dt
   // count is rounded up to a power of two
   int lanes = 1;
   while (lanes < 32 && (n_state + lanes - 1) / lanes > SEL_PER_LANE) lanes <<= 1;
+  // ... then more lanes (down to one state a lane) while one request's blocks would not fill the SMs
+  while (lanes < 32 && lanes < n_state && (long long)inner * lanes < (long long)SEL_BLOCKS * SEL_THREADS) lanes <<= 1;
   int npl = 1;
   while (npl * lanes < n_state) npl <<= 1;
   if (npl > SEL_PER_LANE) return TS_ERR_SIZE;
   const int channels = SEL_THREADS / lanes;
+  int batch = SEL_BATCH;
+  while (batch > 4 && (size_t)batch * (4 * channels + 2 * lanes * npl) * sizeof(float) > SEL_SMEM) batch >>= 1;
   dim3 grid(num_seqs, (inner + channels - 1) / channels);
   if (grid.y > 65535) return TS_ERR_SIZE;
-  const size_t smem = (size_t)SEL_BATCH * (3 * channels + 2 * lanes * npl) * sizeof(float);
+  const size_t smem = (size_t)batch * (4 * channels + 2 * lanes * npl) * sizeof(float);
 #define SEL_LAUNCH(N)                                                                                                    \
   ts_launch(selective_scan_kernel<T, N>, grid, dim3(SEL_THREADS), smem, stream, x, x_stride, dt_raw, dt_bias, bc, bc_stride, \
-            b_first, c_first, a_log, d_skip, z, z_stride, state, out, out_stride, query_start, slots, inner, n_state, lanes)
+            b_first, c_first, a_log, d_skip, z, z_stride, state, out, out_stride, query_start, slots, inner, n_state, lanes, batch)
   switch (npl) {
     case 1: SEL_LAUNCH(1); break;
     case 2: SEL_LAUNCH(2); break;
