@@ -13,6 +13,7 @@ from .model_spec import LayerRun, LayerSpec, ModelSpec, PartSpec, TensorNames
 from .baporax import BaporaxConfig
 from .begovik import BegovikConfig
 from .filezen import FilezenConfig
+from .lorozen import LorozenConfig
 from .qwen2 import Qwen2Config, UnsupportedModelError
 from .registry import (
     UnknownArchitectureError,
@@ -28,7 +29,7 @@ from .registry import (
 __all__ = [
     "EngineConfig", "FinishReason", "RequestOutput", "RequestTiming", "SamplingParams",
     "SchedulerConfig", "resolve_dtype", "LayerRun", "LayerSpec", "ModelSpec", "PartSpec",
-    "TensorNames", "BaporaxConfig", "BegovikConfig", "FilezenConfig", "Qwen2Config", "UnsupportedModelError", "UnknownArchitectureError",
+    "TensorNames", "BaporaxConfig", "BegovikConfig", "FilezenConfig", "LorozenConfig", "Qwen2Config", "UnsupportedModelError", "UnknownArchitectureError",
     "config_from_dict", "config_from_dir", "lookup", "read_config_json",
     "register_architecture", "registered_architectures", "unregister_architecture",
 ]

@@ -59,6 +59,10 @@ class LayerSpec:
     mixer_norm: PartSpec
     feed_forward_norm: PartSpec | None
     position: PartSpec | None = None
+    mixer_output_norm: PartSpec | None = None
+    feed_forward_output_norm: PartSpec | None = None
+    """Norms behind the sublayers, for blocks that have norms on both sides; handed to the block's constructor as
+    ``mixer_output_norm=`` and ``feed_forward_output_norm=``."""
     block: str = "pre_norm"
     block_params: Mapping[str, Any] = field(default_factory=dict)
     """Constants of the arrangement itself (a factor on what is added to the stream, for instance)."""
@@ -81,6 +85,9 @@ class LayerRun:
     layer: int
     cache_from: int | None = None
     shift: int | None = None
+    readds_embedding: bool = False
+    """The embedding's output (the stream as it was before the first layer, a row a token) is added to the stream
+    right before the run."""
 
 
 @dataclass(frozen=True)
@@ -104,6 +111,8 @@ class TensorNames:
     feed_forward: str = "mlp."
     mixer_norm: str = "input_layernorm."
     feed_forward_norm: str = "post_attention_layernorm."
+    mixer_output_norm: str = "post_mixer_layernorm."
+    feed_forward_output_norm: str = "post_feedforward_layernorm."
     prefix_rewrites: tuple[tuple[str, str], ...] = (
         ("transformer.", "model."),
         ("language_model.model.", "model."),

@@ -52,6 +52,8 @@ def _ensure_builtin() -> None:
         from ..models import filezen  # noqa: F401
     if "Begovik" not in _REGISTRY:
         from ..models import begovik  # noqa: F401
+    if "Lorozen" not in _REGISTRY:
+        from ..models import lorozen  # noqa: F401
 
 
 def architecture_of(data: Mapping[str, Any]) -> str:

@@ -7,7 +7,7 @@
 // Per tile: S = Q K^T by mma.sync m16n8k16 (bf16 in, fp32 out); scale, cap and mask in fp32 (scores are kept in units
 // of log 2, so that every exponential is a power of two); running maximum and sum in fp32; P rounded to bfloat16 as
 // the A operand of O += P V (the value fragments come transposed out of shared memory by ldmatrix).  The sink enters
-// at the end as exp(0 - maximum) in the denominator.
+// at the end as exp(s - maximum) in the denominator, s = 0 or the number the query head has learned (sink_values).
 //
 // Tiles of keys are counted from key 0 (or from the first key the block's rows can see under a window, rounded down
 // to a multiple of 64), and a row's sums run over them in order, so without a window what a position gets does not
@@ -65,7 +65,8 @@ capped_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_str
                             const __nv_bfloat16* __restrict__ v_pages, const int* __restrict__ block_table,
                             int table_stride, const int* __restrict__ query_start, const int* __restrict__ context_lens,
                             int num_seqs, int page_size, int num_heads, int num_kv_heads, int dim, int vdim, int window,
-                            float scale, float softcap, int sink, int* __restrict__ status) {
+                            float scale, float softcap, int sink, const float* __restrict__ sink_values,
+                            int* __restrict__ status) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ int tile_info[2];
   pdl_wait();
@@ -266,13 +267,15 @@ capped_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long q_str
   }
   ca_wait<0>();
 
-  // the denominator (with the sink: one more key that scores 0, so exp(0 - maximum) more), and the rows
+  // the denominator (with the sink: one more key that scores 0, or what its head has learned, so exp(that - maximum)
+  // more), and the rows
+  const float sink_log2 = sink && sink_values ? sink_values[head] * 1.4426950408889634f : 0.0f;
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     float total = sum[r];
     total += __shfl_xor_sync(0xffffffffu, total, 1);
     total += __shfl_xor_sync(0xffffffffu, total, 2);
-    if (sink) total = top[r] == -INFINITY ? 1.0f : total + ca_exp2(-top[r]);
+    if (sink) total = top[r] == -INFINITY ? 1.0f : total + ca_exp2(sink_log2 - top[r]);
     const float inv = total > 0.0f ? 1.0f / total : 0.0f;
     if (my_row[r] < rows) {
       __nv_bfloat16* dst = out + (size_t)(token0 + my_row[r]) * out_stride + (size_t)head * vdim + 2 * t4;
@@ -289,7 +292,8 @@ static int capped_attention_mma_launch(const void* q, long long q_stride, void* 
                                        const void* k_pages, const void* v_pages, const int* block_table, int table_stride,
                                        const int* query_start, const int* context_lens, int num_tokens, int num_seqs,
                                        int page_size, int num_heads, int num_kv_heads, int dim, int vdim, int window,
-                                       float scale, float softcap, int sink, int* status, cudaStream_t stream) {
+                                       float scale, float softcap, int sink, const float* sink_values, int* status,
+                                       cudaStream_t stream) {
   const size_t smem = ((size_t)3 * CA_ROWS * (dim + CA_PAD) + (size_t)2 * CA_KEYS * (vdim + CA_PAD)) * sizeof(__nv_bfloat16);
   auto kernel = capped_attention_mma_kernel<KMAX, VMAX>;
   static bool configured = false;
@@ -301,7 +305,7 @@ static int capped_attention_mma_launch(const void* q, long long q_stride, void* 
   ts_launch(kernel, dim3(tiles, num_heads), dim3(CA_THREADS), smem, stream, (const __nv_bfloat16*)q, q_stride,
             (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table,
             table_stride, query_start, context_lens, num_seqs, page_size, num_heads, num_kv_heads, dim, vdim, window, scale,
-            softcap, sink, status);
+            softcap, sink, sink_values, status);
   return ts_launch_status();
 }
 
@@ -310,7 +314,7 @@ TS_EXPORT int ts_paged_attention_capped_mma(const void* q, long long q_stride, v
                                             int table_stride, const int* query_start, const int* context_lens,
                                             int num_tokens, int num_seqs, int page_size, int num_heads, int num_kv_heads,
                                             int dim, int vdim, int window, float scale, float softcap, int sink,
-                                            int* status, cudaStream_t stream) {
+                                            const float* sink_values, int* status, cudaStream_t stream) {
   if (num_tokens <= 0 || num_seqs <= 0) return 0;
   if (dim < 16 || dim % 16 || vdim < 16 || vdim % 16 || dim > 256 || vdim > 128) return TS_ERR_SIZE;
   if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads || num_heads > 65535) return TS_ERR_SIZE;
@@ -321,7 +325,7 @@ TS_EXPORT int ts_paged_attention_capped_mma(const void* q, long long q_stride, v
 #define CA_CASE(K, V)                                                                                                  \
   return capped_attention_mma_launch<K, V>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride, \
                                            query_start, context_lens, num_tokens, num_seqs, page_size, num_heads,     \
-                                           num_kv_heads, dim, vdim, window, scale, softcap, sink, status, stream)
+                                           num_kv_heads, dim, vdim, window, scale, softcap, sink, sink_values, status, stream)
   if (dim <= 64 && vdim <= 64) CA_CASE(4, 8);
   if (dim <= 128) CA_CASE(8, 16);
   CA_CASE(16, 16);

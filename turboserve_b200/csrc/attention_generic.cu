@@ -31,7 +31,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, long long q_stride, T* _
                                int table_stride, const int* __restrict__ seq_of_token,
                                const int* __restrict__ positions, int page_size, int num_heads,
                                int num_kv_heads, int head_dim, int v_dim, int window, float scale,
-                               float softcap, int sink, int* __restrict__ status) {
+                               float softcap, int sink, const float* __restrict__ sink_values,
+                               int* __restrict__ status) {
   pdl_wait();
   pdl_trigger();
   extern __shared__ float smem[];
@@ -128,9 +129,10 @@ paged_attention_generic_kernel(const T* __restrict__ q, long long q_stride, T* _
     for (int w = 0; w < GENERIC_STREAMS; ++w) m_all = fmaxf(m_all, part_ml[w * 2]);
     float weight[GENERIC_STREAMS];
     float l_all = 0.0f;
-    if (sink) {  // a key whose score is 0 and whose value is nothing: it only adds to the denominator
-      m_all = fmaxf(m_all, 0.0f);
-      l_all = expf(-m_all);
+    if (sink) {  // a key whose value is nothing: it only adds to the denominator; its score is 0 or the head's own
+      const float s0 = sink_values ? sink_values[head] : 0.0f;
+      m_all = fmaxf(m_all, s0);
+      l_all = expf(s0 - m_all);
     }
     for (int w = 0; w < GENERIC_STREAMS; ++w) {
       const float mw = part_ml[w * 2];
@@ -184,7 +186,8 @@ paged_attention_group_kernel(const T* __restrict__ q, long long q_stride, T* __r
                              const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                              const int* __restrict__ block_table, int table_stride, const int* __restrict__ seq_of_token,
                              const int* __restrict__ positions, int page_size, int num_kv_heads, int head_dim, int v_dim,
-                             int window, float scale, float softcap, int sink, int vector_rows, int* __restrict__ status) {
+                             int window, float scale, float softcap, int sink, const float* __restrict__ sink_values,
+                             int vector_rows, int* __restrict__ status) {
   pdl_wait();
   pdl_trigger();
   extern __shared__ __align__(16) float smem[];
@@ -323,8 +326,9 @@ paged_attention_group_kernel(const T* __restrict__ q, long long q_stride, T* __r
     float weight[GENERIC_STREAMS];
     float l_all = 0.0f;
     if (sink) {
-      m_all = fmaxf(m_all, 0.0f);
-      l_all = expf(-m_all);
+      const float s0 = sink_values ? sink_values[kv_head * QH + h] : 0.0f;
+      m_all = fmaxf(m_all, s0);
+      l_all = expf(s0 - m_all);
     }
     for (int w = 0; w < GENERIC_STREAMS; ++w) {
       const float mw = part_ml[(w * QH + h) * 2];
@@ -346,7 +350,7 @@ static int paged_attention_group_launch(const void* q, long long q_stride, void*
                                         const void* k_pages, const void* v_pages, const int* block_table,
                                         int table_stride, const int* seq_of_token, const int* positions, int num_tokens,
                                         int page_size, int num_kv_heads, int head_dim, int v_dim, int window, float scale,
-                                        float softcap, int sink, int* status, cudaStream_t stream) {
+                                        float softcap, int sink, const float* sink_values, int* status, cudaStream_t stream) {
   const size_t floats = (size_t)QH * head_dim + (size_t)GENERIC_STREAMS * QH * v_dim + (size_t)GENERIC_STREAMS * QH * 2 +
                         (size_t)GENERIC_STREAMS * 32 * QH;
   const size_t smem = floats * sizeof(float) + (size_t)GENERIC_STREAMS * 32 * sizeof(unsigned long long);
@@ -356,20 +360,22 @@ static int paged_attention_group_launch(const void* q, long long q_stride, void*
   const int vector_rows = (head_dim * sizeof(T)) % 16 == 0 && !((uintptr_t)k_pages & 15);
   ts_launch(kernel, dim3(num_tokens, num_kv_heads), dim3(GENERIC_STREAMS * 32), smem, stream, (const T*)q, q_stride, (T*)out,
             out_stride, (const T*)k_pages, (const T*)v_pages, block_table, table_stride, seq_of_token, positions, page_size,
-            num_kv_heads, head_dim, v_dim, window, scale, softcap, sink, vector_rows, status);
+            num_kv_heads, head_dim, v_dim, window, scale, softcap, sink, sink_values, vector_rows, status);
   return ts_launch_status();
 }
 
 // The kernel with every option: value rows of their own width (v_dim), scores capped as
 // softcap * tanh(score / softcap) (softcap 0: as they are), and a sink (sink != 0: the softmax's
-// denominator is one larger, as if one more key scored 0 and had no value).
+// denominator holds one more term, as if one more key had no value; it scores 0, or, with sink_values,
+// the number its query head has learned: exp(sink_values[head]), neither scaled nor capped).
 TS_EXPORT int ts_paged_attention_capped(int dtype, const void* q, long long q_stride, void* out,
                                         long long out_stride, const void* k_pages,
                                         const void* v_pages, const int* block_table,
                                         int table_stride, const int* seq_of_token,
                                         const int* positions, int num_tokens, int page_size,
                                         int num_heads, int num_kv_heads, int head_dim, int v_dim, int window,
-                                        float scale, float softcap, int sink, int* status, cudaStream_t stream) {
+                                        float scale, float softcap, int sink, const float* sink_values, int* status,
+                                        cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (head_dim < 1 || head_dim > 32 * MAX_DIMS_PER_LANE || v_dim < 1 || v_dim > 32 * MAX_DIMS_PER_LANE) return TS_ERR_SIZE;
   if (num_heads < 1 || num_kv_heads < 1 || num_heads % num_kv_heads) return TS_ERR_SIZE;
@@ -384,11 +390,11 @@ TS_EXPORT int ts_paged_attention_capped(int dtype, const void* q, long long q_st
                ? paged_attention_group_launch<float, HEADS>(q, q_stride, out, out_stride, k_pages, v_pages, block_table, \
                                                             table_stride, seq_of_token, positions, num_tokens, page_size, \
                                                             num_kv_heads, head_dim, v_dim, window, scale, softcap, sink, \
-                                                            status, stream)                                              \
+                                                            sink_values, status, stream)                                              \
                : paged_attention_group_launch<__nv_bfloat16, HEADS>(q, q_stride, out, out_stride, k_pages, v_pages,     \
                                                                     block_table, table_stride, seq_of_token, positions, \
                                                                     num_tokens, page_size, num_kv_heads, head_dim, v_dim, \
-                                                                    window, scale, softcap, sink, status, stream)
+                                                                    window, scale, softcap, sink, sink_values, status, stream)
     switch (per_group) {
       GROUP_CASE(1); GROUP_CASE(2); GROUP_CASE(3); GROUP_CASE(4); GROUP_CASE(5); GROUP_CASE(6); GROUP_CASE(7); GROUP_CASE(8);
     }
@@ -402,13 +408,13 @@ TS_EXPORT int ts_paged_attention_capped(int dtype, const void* q, long long q_st
     ts_launch(paged_attention_generic_kernel<float>, dim3(grid), dim3(threads), smem, stream, 
         (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pages,
         (const float*)v_pages, block_table, table_stride, seq_of_token, positions, page_size,
-        num_heads, num_kv_heads, head_dim, v_dim, window, scale, softcap, sink, status);
+        num_heads, num_kv_heads, head_dim, v_dim, window, scale, softcap, sink, sink_values, status);
   else if (dtype == TS_BF16)
     ts_launch(paged_attention_generic_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), smem, stream, 
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
         (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_table, table_stride,
         seq_of_token, positions, page_size, num_heads, num_kv_heads, head_dim, v_dim, window, scale,
-        softcap, sink, status);
+        softcap, sink, sink_values, status);
   else
     return TS_ERR_DTYPE;
   return ts_launch_status();
@@ -423,5 +429,5 @@ TS_EXPORT int ts_paged_attention_generic(int dtype, const void* q, long long q_s
                                          float scale, int* status, cudaStream_t stream) {
   return ts_paged_attention_capped(dtype, q, q_stride, out, out_stride, k_pages, v_pages, block_table, table_stride,
                                    seq_of_token, positions, num_tokens, page_size, num_heads, num_kv_heads, head_dim,
-                                   head_dim, window, scale, 0.0f, 0, status, stream);
+                                   head_dim, window, scale, 0.0f, 0, nullptr, status, stream);
 }

@@ -9,7 +9,7 @@
 //                     part and of every head's rotated query part (fp32 angles, cos and sin times a
 //                     constant), append of [c | r] to the request's pages
 //   head_linear       out[t, h, :] = W[h] in[t, h, :] for all heads in one launch (q_plain -> q~, and
-//                     sum p c -> the head's value), fp32 accumulation
+//                     sum p c -> the head's value), fp32 accumulation; optionally times sigmoid(gate[t, h])
 //   latent_attention  softmax attention of every (token, head) over the cached rows of its window; the
 //                     value of a key is the first `rank` elements of its row
 //   latent_gather     the rows of a range of positions of one request, from its pages into one matrix
@@ -131,7 +131,8 @@ TS_EXPORT int ts_latent_prepare(int dtype, void* q, long long q_stride, const vo
 template <typename T>
 __global__ void __launch_bounds__(256)
 head_linear_kernel(const T* __restrict__ in, long long in_stride, int in_head, const T* __restrict__ w,
-                   T* __restrict__ out, long long out_stride, int out_head, int m, int n, int k) {
+                   T* __restrict__ out, long long out_stride, int out_head, int m, int n, int k,
+                   const T* __restrict__ gate, long long gate_stride) {
   pdl_wait();
   pdl_trigger();
   __shared__ float a_s[HL_K][HL_M + 4];
@@ -174,26 +175,29 @@ head_linear_kernel(const T* __restrict__ in, long long in_stride, int in_head, c
   for (int i = 0; i < 4; ++i) {
     const int row = tile_m + ty * 4 + i;
     if (row >= m) continue;
+    // a gate per (row, head): the head's outputs times the sigmoid of one number, in fp32 before the rounding
+    const float open = gate ? 1.0f / (1.0f + expf(-to_float(gate[(size_t)row * gate_stride + head]))) : 1.0f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int col = tile_n + tx * 4 + j;
-      if (col < n) out[(size_t)row * out_stride + (size_t)head * out_head + col] = from_float<T>(acc[i][j]);
+      if (col < n) out[(size_t)row * out_stride + (size_t)head * out_head + col] = from_float<T>(acc[i][j] * open);
     }
   }
 }
 
 TS_EXPORT int ts_head_linear(int dtype, const void* in, long long in_stride, int in_head, const void* w, void* out,
                              long long out_stride, int out_head, int m, int heads, int n, int k,
-                             cudaStream_t stream) {
+                             const void* gate, long long gate_stride, cudaStream_t stream) {
   if (m <= 0 || n <= 0 || heads <= 0) return 0;
   if (k < 0 || heads > 65535 || (m + HL_M - 1) / HL_M > 65535) return TS_ERR_SIZE;
   dim3 grid((n + HL_N - 1) / HL_N, (m + HL_M - 1) / HL_M, heads);
   if (dtype == TS_F32)
     ts_launch(head_linear_kernel<float>, grid, dim3(256), 0, stream, (const float*)in, in_stride, in_head,
-              (const float*)w, (float*)out, out_stride, out_head, m, n, k);
+              (const float*)w, (float*)out, out_stride, out_head, m, n, k, (const float*)gate, gate_stride);
   else if (dtype == TS_BF16)
     ts_launch(head_linear_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)in, in_stride,
-              in_head, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, out_stride, out_head, m, n, k);
+              in_head, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, out_stride, out_head, m, n, k,
+              (const __nv_bfloat16*)gate, gate_stride);
   else
     return TS_ERR_DTYPE;
   return ts_launch_status();

@@ -588,7 +588,7 @@ TS_EXPORT int ts_rope_cache_write(int dtype, void* qkv, long long row_stride, co
 #define HEAD_PREPARE_WARPS 8
 template <typename T>
 __global__ void __launch_bounds__(32 * HEAD_PREPARE_WARPS)
-head_norm_rope_write_kernel(T* __restrict__ qkv, long long row_stride, const float* __restrict__ q_gain,
+head_norm_rope_write_kernel(T* __restrict__ qkv, long long row_stride, const float* __restrict__ bias, const float* __restrict__ q_gain,
                             const float* __restrict__ k_gain, float eps, const int* __restrict__ positions,
                             const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int table_stride,
                             T* __restrict__ k_pages, T* __restrict__ v_pages, int page_size, int num_heads,
@@ -604,8 +604,10 @@ head_norm_rope_write_kernel(T* __restrict__ qkv, long long row_stride, const flo
   const int pos = positions[t];
   const bool is_q = head < num_heads, is_k = !is_q && head < num_heads + num_kv_heads;
   const int width = (is_q || is_k) ? dim : vdim;
-  T* x = qkv + (size_t)t * row_stride +
-         (is_q || is_k ? (size_t)head * dim : (size_t)(num_heads + num_kv_heads) * dim + (size_t)(head - num_heads - num_kv_heads) * vdim);
+  const size_t column =
+      is_q || is_k ? (size_t)head * dim : (size_t)(num_heads + num_kv_heads) * dim + (size_t)(head - num_heads - num_kv_heads) * vdim;
+  T* x = qkv + (size_t)t * row_stride + column;
+  const float* b = bias ? bias + column : nullptr;  // the projection's bias, added here in fp32
   T* dst = x;
   if (!is_q) {
     if (!write_kv) return;
@@ -619,14 +621,18 @@ head_norm_rope_write_kernel(T* __restrict__ qkv, long long row_stride, const flo
                : v_pages + (place * num_kv_heads + (head - num_heads - num_kv_heads)) * vdim;
   }
   if (!is_q && !is_k) {
-    for (int i = lane; i < width; i += 32) dst[i] = x[i];
+    if (b) {
+      for (int i = lane; i < width; i += 32) dst[i] = from_float<T>(to_float(x[i]) + b[i]);
+    } else {
+      for (int i = lane; i < width; i += 32) dst[i] = x[i];
+    }
     return;
   }
   float* h = heads_s[warp];
   const float* gain = is_q ? q_gain : k_gain;
   float sum_sq = 0.0f;
   for (int i = lane; i < dim; i += 32) {
-    const float v = to_float(x[i]);
+    const float v = to_float(x[i]) + (b ? b[i] : 0.0f);
     h[i] = v;
     sum_sq = fmaf(v, v, sum_sq);
   }
@@ -648,7 +654,7 @@ head_norm_rope_write_kernel(T* __restrict__ qkv, long long row_stride, const flo
   for (int i = rotary_dim + lane; i < dim; i += 32) dst[i] = from_float<T>(h[i]);
 }
 
-TS_EXPORT int ts_head_norm_rope_write(int dtype, void* qkv, long long row_stride, const float* q_gain, const float* k_gain,
+TS_EXPORT int ts_head_norm_rope_write(int dtype, void* qkv, long long row_stride, const float* bias, const float* q_gain, const float* k_gain,
                                       float eps, const int* positions, const int* seq_of_token, const int* block_table,
                                       int table_stride, void* k_pages, void* v_pages, int page_size, int num_tokens,
                                       int num_heads, int num_kv_heads, int dim, int vdim, const float* inv_freq,
@@ -663,11 +669,11 @@ TS_EXPORT int ts_head_norm_rope_write(int dtype, void* qkv, long long row_stride
   dim3 grid(num_tokens, (heads + HEAD_PREPARE_WARPS - 1) / HEAD_PREPARE_WARPS);
   if (dtype == TS_F32)
     ts_launch(head_norm_rope_write_kernel<float>, grid, dim3(32 * HEAD_PREPARE_WARPS), 0, stream, (float*)qkv, row_stride,
-              q_gain, k_gain, eps, positions, seq_of_token, block_table, table_stride, (float*)k_pages, (float*)v_pages,
+              bias, q_gain, k_gain, eps, positions, seq_of_token, block_table, table_stride, (float*)k_pages, (float*)v_pages,
               page_size, num_heads, num_kv_heads, dim, vdim, inv_freq, rotary_dim, interleaved, write_kv, status);
   else if (dtype == TS_BF16)
     ts_launch(head_norm_rope_write_kernel<__nv_bfloat16>, grid, dim3(32 * HEAD_PREPARE_WARPS), 0, stream,
-              (__nv_bfloat16*)qkv, row_stride, q_gain, k_gain, eps, positions, seq_of_token, block_table, table_stride,
+              (__nv_bfloat16*)qkv, row_stride, bias, q_gain, k_gain, eps, positions, seq_of_token, block_table, table_stride,
               (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, page_size, num_heads, num_kv_heads, dim, vdim, inv_freq,
               rotary_dim, interleaved, write_kv, status);
   else

@@ -1,9 +1,14 @@
 // Mixture of experts: the router, and the experts' products for steps of few tokens and of many.
 //
-//   moe_route      per token: logits z = W_r h in fp32 (W_r is kept in fp32), s = softmax(z) over all experts,
+//   moe_route      per token: logits z = W_r h in fp32 (W_r is kept in fp32), s = softmax(z) over all experts
+//                  (or, mode bit 0, s = sigmoid(z), every expert on its own),
 //                  experts in `groups` equal groups of neighbours of which only the `keep` groups with the
 //                  largest maximum may be chosen from, the `top` largest allowed scores, and their weights
-//                  s / (sum of the chosen s + 1e-20).  Ties go to the lower index.
+//                  s / (sum of the chosen s + 1e-20) (or, mode bit 1, the chosen s as they are).  Ties go to
+//                  the lower index.
+//   A weight may stand on the expert's OUTPUT (the kernels that add the experts' rows up take `weights`) or on its
+//   INPUT, expert(w h) (the kernels that make gate and up take `in_weights`: gate (w h) = w (gate h), so the factor
+//   enters in fp32 on the sums, before the rounding and the activation; the adding kernels then get no weights).
 //   Few tokens (every request brings one): no sorting, every (token, chosen expert) pair streams its expert's rows
 //     moe_pair_gate_up   hidden[pair, f] = act(gate_e[f] . h) * (up_e[f] . h), a warp per feature
 //     moe_pair_down      out[t] = sum_k weight_k * (down_{e_k} hidden[t, k]) (+ addend[t]), a warp per output,
@@ -25,7 +30,7 @@
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const T* __restrict__ x, long long x_stride, const float* __restrict__ router, int width, int experts,
-                 int top, int groups, int keep, int* __restrict__ chosen, float* __restrict__ weights) {
+                 int top, int groups, int keep, int mode, int* __restrict__ chosen, float* __restrict__ weights) {
   extern __shared__ float mr_smem[];
   float* h = mr_smem;            // [width]
   float* score = h + width;      // [experts]
@@ -45,14 +50,17 @@ moe_route_kernel(const T* __restrict__ x, long long x_stride, const float* __res
   }
   __syncthreads();
   if (warp != 0) return;
-  // softmax over all experts
-  float biggest = -INFINITY;
-  for (int e = lane; e < experts; e += 32) biggest = fmaxf(biggest, score[e]);
-  biggest = warp_max(biggest);
-  float total = 0.0f;
-  for (int e = lane; e < experts; e += 32) total += expf(score[e] - biggest);
-  total = warp_sum(total);
-  for (int e = lane; e < experts; e += 32) score[e] = expf(score[e] - biggest) / total;
+  if (mode & 1) {  // every expert's score on its own
+    for (int e = lane; e < experts; e += 32) score[e] = 1.0f / (1.0f + expf(-score[e]));
+  } else {  // softmax over all experts
+    float biggest = -INFINITY;
+    for (int e = lane; e < experts; e += 32) biggest = fmaxf(biggest, score[e]);
+    biggest = warp_max(biggest);
+    float total = 0.0f;
+    for (int e = lane; e < experts; e += 32) total += expf(score[e] - biggest);
+    total = warp_sum(total);
+    for (int e = lane; e < experts; e += 32) score[e] = expf(score[e] - biggest) / total;
+  }
   __syncwarp();
   const int per_group = experts / groups;
   if (groups > 1 && keep < groups) {
@@ -107,13 +115,13 @@ moe_route_kernel(const T* __restrict__ x, long long x_stride, const float* __res
     }
     for (int k = 0; k < top; ++k) {
       chosen[(size_t)t * top + k] = picked[k];
-      weights[(size_t)t * top + k] = picked_score[k] / (sum + 1e-20f);
+      weights[(size_t)t * top + k] = (mode & 2) ? picked_score[k] : picked_score[k] / (sum + 1e-20f);
     }
   }
 }
 
 TS_EXPORT int ts_moe_route(int dtype, const void* x, long long x_stride, const float* router, int num_tokens,
-                           int width, int experts, int top, int groups, int keep, int* chosen, float* weights,
+                           int width, int experts, int top, int groups, int keep, int mode, int* chosen, float* weights,
                            cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   if (experts < 1 || top < 1 || top > MOE_MAX_TOP || top > experts || groups < 1 || experts % groups || keep < 1 ||
@@ -124,12 +132,12 @@ TS_EXPORT int ts_moe_route(int dtype, const void* x, long long x_stride, const f
   if (dtype == TS_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ts_launch(moe_route_kernel<float>, dim3(num_tokens), dim3(128), smem, stream, (const float*)x, x_stride, router, width,
-              experts, top, groups, keep, chosen, weights);
+              experts, top, groups, keep, mode, chosen, weights);
   } else if (dtype == TS_BF16) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ts_launch(moe_route_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(128), smem, stream, (const __nv_bfloat16*)x, x_stride,
-              router, width, experts, top, groups, keep, chosen, weights);
+              router, width, experts, top, groups, keep, mode, chosen, weights);
   } else {
     return TS_ERR_DTYPE;
   }
@@ -177,7 +185,8 @@ template <> __device__ __forceinline__ float row_dot<__nv_bfloat16>(const __nv_b
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_pair_gate_up_kernel(const T* __restrict__ x, long long x_stride, const T* __restrict__ gate_up,
-                        const int* __restrict__ chosen, T* __restrict__ hidden, int width, int ff, int top, int act) {
+                        const int* __restrict__ chosen, const float* __restrict__ in_weights, T* __restrict__ hidden,
+                        int width, int ff, int top, int act) {
   extern __shared__ float mp_smem[];  // [width]
   const int pair = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
   pdl_wait();
@@ -186,18 +195,19 @@ moe_pair_gate_up_kernel(const T* __restrict__ x, long long x_stride, const T* __
   for (int i = threadIdx.x; i < width; i += blockDim.x) mp_smem[i] = to_float(row[i]);
   __syncthreads();
   const int expert = chosen[pair];
+  const float scale_in = in_weights ? in_weights[pair] : 1.0f;
   const T* base = gate_up + (size_t)expert * 2 * ff * width;
   const int f_end = min(ff, (int)(blockIdx.y + 1) * MOE_FEATURES_PER_BLOCK);
   for (int f = blockIdx.y * MOE_FEATURES_PER_BLOCK + warp; f < f_end; f += warps) {
     // gate and up are rounded to the activation type first, as a product that writes them would
-    const float g = to_float(from_float<T>(row_dot<T>(base + (size_t)f * width, mp_smem, width, lane)));
-    const float u = to_float(from_float<T>(row_dot<T>(base + (size_t)(ff + f) * width, mp_smem, width, lane)));
+    const float g = to_float(from_float<T>(scale_in * row_dot<T>(base + (size_t)f * width, mp_smem, width, lane)));
+    const float u = to_float(from_float<T>(scale_in * row_dot<T>(base + (size_t)(ff + f) * width, mp_smem, width, lane)));
     if (lane == 0) hidden[(size_t)pair * ff + f] = from_float<T>(activation(g, act) * u);
   }
 }
 
 TS_EXPORT int ts_moe_pair_gate_up(int dtype, const void* x, long long x_stride, const void* gate_up, const int* chosen,
-                                  void* hidden, int num_tokens, int width, int ff, int top, int act,
+                                  const float* in_weights, void* hidden, int num_tokens, int width, int ff, int top, int act,
                                   cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
   const size_t smem = (size_t)width * sizeof(float);
@@ -207,12 +217,12 @@ TS_EXPORT int ts_moe_pair_gate_up(int dtype, const void* x, long long x_stride, 
   if (dtype == TS_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_pair_gate_up_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ts_launch(moe_pair_gate_up_kernel<float>, grid, dim3(256), smem, stream, (const float*)x, x_stride, (const float*)gate_up,
-              chosen, (float*)hidden, width, ff, top, act);
+              chosen, in_weights, (float*)hidden, width, ff, top, act);
   } else if (dtype == TS_BF16) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(moe_pair_gate_up_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ts_launch(moe_pair_gate_up_kernel<__nv_bfloat16>, grid, dim3(256), smem, stream, (const __nv_bfloat16*)x, x_stride,
-              (const __nv_bfloat16*)gate_up, chosen, (__nv_bfloat16*)hidden, width, ff, top, act);
+              (const __nv_bfloat16*)gate_up, chosen, in_weights, (__nv_bfloat16*)hidden, width, ff, top, act);
   } else {
     return TS_ERR_DTYPE;
   }
@@ -237,7 +247,7 @@ moe_pair_down_kernel(const T* __restrict__ hidden, const T* __restrict__ down, c
     for (int k = 0; k < top; ++k) {
       const int expert = chosen[(size_t)t * top + k];
       const float part = row_dot<T>(down + ((size_t)expert * width + o) * ff, mp_smem + (size_t)k * ff, ff, lane);
-      sum = fmaf(weights[(size_t)t * top + k], to_float(from_float<T>(part)), sum);
+      sum = fmaf(weights ? weights[(size_t)t * top + k] : 1.0f, to_float(from_float<T>(part)), sum);
     }
     if (lane == 0) {
       if (addend) sum += to_float(addend[(size_t)t * width + o]);
@@ -420,7 +430,7 @@ template <typename T, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_expert_rows_kernel(const T* __restrict__ in, long long in_stride, const T* __restrict__ weights,
                        const int* __restrict__ counters, const int* __restrict__ pair_of_row, T* __restrict__ out, int k,
-                       int n_out, int top, int experts, int act) {
+                       int n_out, int top, int experts, int act, const float* __restrict__ in_weights) {
   extern __shared__ __align__(16) unsigned char me_smem[];
   T* rows_s = reinterpret_cast<T*>(me_smem);  // [ME_ROWS][k]
   const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
@@ -472,8 +482,10 @@ moe_expert_rows_kernel(const T* __restrict__ in, long long in_stride, const T* _
             if (GATED) other = b[r];
           }
         float result = mine;
-        if (GATED)  // gate and up are rounded to the activation type first, as a product that writes them would
-          result = activation(to_float(from_float<T>(mine)), act) * to_float(from_float<T>(other));
+        if (GATED) {  // gate and up are rounded to the activation type first, as a product that writes them would
+          const float scale_in = in_weights ? in_weights[pair_of_row[first + chunk + lane]] : 1.0f;
+          result = activation(to_float(from_float<T>(scale_in * mine)), act) * to_float(from_float<T>(scale_in * other));
+        }
         out[(size_t)(first + chunk + lane) * n_out + f] = from_float<T>(result);
       }
     }
@@ -502,7 +514,7 @@ __global__ void __launch_bounds__(32 * MT_GROUPS * MT_SLICES, NT == 1 ? 2 : 1)
 moe_expert_rows_mma_kernel(const __nv_bfloat16* __restrict__ in, long long in_stride,
                            const __nv_bfloat16* __restrict__ weights, const int* __restrict__ counters,
                            const int* __restrict__ pair_of_row, __nv_bfloat16* __restrict__ out, int k, int n_out, int top,
-                           int experts, int act) {
+                           int experts, int act, const float* __restrict__ in_weights) {
   constexpr int ROWS = 8 * NT;
   extern __shared__ __align__(16) unsigned char me_smem[];
   __nv_bfloat16* rows_s = reinterpret_cast<__nv_bfloat16*>(me_smem);  // [ROWS][k + 32]: rows 64 bytes apart in banks
@@ -598,7 +610,8 @@ moe_expert_rows_mma_kernel(const __nv_bfloat16* __restrict__ in, long long in_st
         if (feature >= n_out || r >= rows) continue;
         float result = sum;
         if (GATED) {
-          const float gate = __bfloat162float(__float2bfloat16_rn(sum)), upv = __bfloat162float(__float2bfloat16_rn(sum2));
+          const float scale_in = in_weights ? in_weights[pair_of_row[first + chunk + r]] : 1.0f;
+          const float gate = __bfloat162float(__float2bfloat16_rn(scale_in * sum)), upv = __bfloat162float(__float2bfloat16_rn(scale_in * sum2));
           result = activation(gate, act) * upv;
         }
         out[(size_t)(first + chunk + r) * n_out + feature] = __float2bfloat16_rn(result);
@@ -609,7 +622,7 @@ moe_expert_rows_mma_kernel(const __nv_bfloat16* __restrict__ in, long long in_st
 template <bool GATED, int NT>
 static int launch_expert_rows_mma(const void* in, long long in_stride, const void* weights, const int* counters,
                                   const int* pair_of_row, void* out, int k, int n_out, int top, int experts, int act,
-                                  cudaStream_t stream) {
+                                  const float* in_weights, cudaStream_t stream) {
   const size_t smem = (size_t)8 * NT * (k + 32) * 2 + (size_t)MT_SLICES * MT_GROUPS * 32 * 8 * NT * sizeof(float);
   dim3 tiles(experts, (n_out + 16 * MT_GROUPS - 1) / (16 * MT_GROUPS));
   if (tiles.y > 65535 || smem > 200 * 1024) return TS_ERR_SIZE;
@@ -617,14 +630,15 @@ static int launch_expert_rows_mma(const void* in, long long in_stride, const voi
     cudaFuncSetAttribute(moe_expert_rows_mma_kernel<GATED, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   ts_launch(moe_expert_rows_mma_kernel<GATED, NT>, tiles, dim3(32 * MT_GROUPS * MT_SLICES), smem, stream,
             (const __nv_bfloat16*)in, in_stride, (const __nv_bfloat16*)weights, counters, pair_of_row, (__nv_bfloat16*)out, k,
-            n_out, top, experts, act);
+            n_out, top, experts, act, in_weights);
   return ts_launch_status();
 }
 
 // in: the step's inputs [tokens][in_stride] (gated) or the rows of the gated call [pairs][k] (plain).
 TS_EXPORT int ts_moe_expert_rows(int dtype, int gated, const void* in, long long in_stride, const void* weights,
                                  const int* counters, const int* pair_of_row, void* out, int k, int n_out, int top,
-                                 int experts, int num_pairs, int act, cudaStream_t stream) {
+                                 int experts, int num_pairs, int act, const float* in_weights, cudaStream_t stream) {
+  if (!gated) in_weights = nullptr;
   if (experts <= 0 || n_out <= 0) return 0;
   const size_t item = dtype == TS_F32 ? 4 : 2;
   const size_t smem = (size_t)ME_ROWS * k * item;
@@ -633,11 +647,11 @@ TS_EXPORT int ts_moe_expert_rows(int dtype, int gated, const void* in, long long
     // experts with more than eight rows each on average take sixteen rows a pass, where shared memory has the room
     int code = TS_ERR_SIZE;
     if (num_pairs > 8 * experts)
-      code = gated ? launch_expert_rows_mma<true, 2>(in, in_stride, weights, counters, pair_of_row, out, k, n_out, top, experts, act, stream)
-                   : launch_expert_rows_mma<false, 2>(in, in_stride, weights, counters, pair_of_row, out, k, n_out, top, experts, act, stream);
+      code = gated ? launch_expert_rows_mma<true, 2>(in, in_stride, weights, counters, pair_of_row, out, k, n_out, top, experts, act, in_weights, stream)
+                   : launch_expert_rows_mma<false, 2>(in, in_stride, weights, counters, pair_of_row, out, k, n_out, top, experts, act, in_weights, stream);
     if (code == TS_ERR_SIZE)
-      code = gated ? launch_expert_rows_mma<true, 1>(in, in_stride, weights, counters, pair_of_row, out, k, n_out, top, experts, act, stream)
-                   : launch_expert_rows_mma<false, 1>(in, in_stride, weights, counters, pair_of_row, out, k, n_out, top, experts, act, stream);
+      code = gated ? launch_expert_rows_mma<true, 1>(in, in_stride, weights, counters, pair_of_row, out, k, n_out, top, experts, act, in_weights, stream)
+                   : launch_expert_rows_mma<false, 1>(in, in_stride, weights, counters, pair_of_row, out, k, n_out, top, experts, act, in_weights, stream);
     if (code != TS_ERR_SIZE) return code;
   }
   dim3 grid(experts, (n_out + ME_FEATURES_PER_BLOCK - 1) / ME_FEATURES_PER_BLOCK);
@@ -647,7 +661,7 @@ TS_EXPORT int ts_moe_expert_rows(int dtype, int gated, const void* in, long long
     if (smem > 48 * 1024)                                                                                              \
       cudaFuncSetAttribute(moe_expert_rows_kernel<TYPE, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
     ts_launch(moe_expert_rows_kernel<TYPE, G>, grid, dim3(256), smem, stream, (const TYPE*)in, in_stride,              \
-              (const TYPE*)weights, counters, pair_of_row, (TYPE*)out, k, n_out, top, experts, act);                   \
+              (const TYPE*)weights, counters, pair_of_row, (TYPE*)out, k, n_out, top, experts, act, in_weights);       \
   } while (0)
   if (dtype == TS_F32) {
     if (gated) ME_LAUNCH(float, true); else ME_LAUNCH(float, false);
@@ -678,24 +692,30 @@ TS_EXPORT int ts_moe_sort(const int* chosen, int pairs, int experts, int* counte
 
 template <typename T>
 __global__ void moe_gather_kernel(const T* __restrict__ x, long long x_stride, const int* __restrict__ pair_of_row,
-                                  T* __restrict__ rows, int width, int top) {
+                                  T* __restrict__ rows, int width, int top, const float* __restrict__ in_weights) {
   pdl_wait();
   pdl_trigger<1>();
   const int r = blockIdx.x;
-  const T* src = x + (size_t)(pair_of_row[r] / top) * x_stride;
+  const int pair = pair_of_row[r];
+  const T* src = x + (size_t)(pair / top) * x_stride;
   T* dst = rows + (size_t)r * width;
+  if (in_weights) {  // the expert reads its token's row times the pair's weight
+    const float w = in_weights[pair];
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = from_float<T>(w * to_float(src[i]));
+    return;
+  }
   for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src[i];
 }
 
 TS_EXPORT int ts_moe_gather(int dtype, const void* x, long long x_stride, const int* pair_of_row, void* rows, int pairs,
-                            int width, int top, cudaStream_t stream) {
+                            int width, int top, const float* in_weights, cudaStream_t stream) {
   if (pairs <= 0) return 0;
   if (dtype == TS_F32)
     ts_launch(moe_gather_kernel<float>, dim3(pairs), dim3(128), 0, stream, (const float*)x, x_stride, pair_of_row,
-              (float*)rows, width, top);
+              (float*)rows, width, top, in_weights);
   else if (dtype == TS_BF16)
     ts_launch(moe_gather_kernel<__nv_bfloat16>, dim3(pairs), dim3(128), 0, stream, (const __nv_bfloat16*)x, x_stride,
-              pair_of_row, (__nv_bfloat16*)rows, width, top);
+              pair_of_row, (__nv_bfloat16*)rows, width, top, in_weights);
   else
     return TS_ERR_DTYPE;
   return ts_launch_status();
@@ -711,7 +731,7 @@ __global__ void moe_combine_kernel(const T* __restrict__ rows, const int* __rest
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float sum = 0.0f;
     for (int k = 0; k < top; ++k)
-      sum = fmaf(weights[(size_t)t * top + k], to_float(rows[(size_t)place[(size_t)t * top + k] * width + i]), sum);
+      sum = fmaf(weights ? weights[(size_t)t * top + k] : 1.0f, to_float(rows[(size_t)place[(size_t)t * top + k] * width + i]), sum);
     if (addend) sum += to_float(addend[(size_t)t * width + i]);
     out[(size_t)t * width + i] = from_float<T>(sum);
   }

@@ -12,8 +12,11 @@
 //   norm_add      residual += mult * (update * rsqrt(mean(update^2) + eps) * gain), the norm taken on a
 //                 sublayer's OUTPUT, all in fp32; the new residual is also written in the activation
 //                 type as the next sublayer's input.  Without an update it only writes that copy.
+//   norm_add_norm norm_add for the sublayer that ran, an optional matrix of fp32 rows added, and the norm before the
+//                 sublayer that runs next, in one pass over the row (a block with norms on both sides of its sublayers).
 //   activation    out = act(in), act one of relu^2, gelu(tanh), silu, tanh, in fp32, rounded once.
 //   scale_rows    fp32 rows times a constant, in place (a head whose logits are scaled).
+//   softcap_rows  fp32 rows through cap * tanh(x / cap), in place (a head whose logits are capped).
 #include "common.cuh"
 
 template <typename T>
@@ -144,6 +147,78 @@ TS_EXPORT int ts_norm_add(int dtype, float* residual, const void* update, const 
   return ts_launch_status();
 }
 
+// A block with norms before AND behind its sublayers: what stands between two sublayers is one kernel,
+//     residual += update * rsqrt(mean(update^2) + eps_post) * gain_post      (the norm behind the sublayer that ran)
+//     residual += extra                                                      (fp32 rows, e.g. the embedding's output
+//                                                                             that a repeated stretch adds before a pass)
+//     out = residual * rsqrt(mean(residual^2) + eps_pre) * gain_pre          (the norm before the sublayer that runs next)
+// each part optional, everything in fp32, `out` rounded once.  With `rows` the listed rows alone are worked and the
+// residual is left as it is (the final norm, at the rows whose logits are wanted).  One block per row; a thread meets
+// the same elements in every pass, so the row lives in shared memory without a barrier of its own.
+template <typename T>
+__global__ void norm_add_norm_kernel(float* __restrict__ residual, const T* __restrict__ update,
+                                     const float* __restrict__ gain_post, float eps_post, const float* __restrict__ extra,
+                                     const float* __restrict__ gain_pre, float eps_pre, T* __restrict__ out,
+                                     const int* __restrict__ rows, int hidden) {
+  extern __shared__ __align__(16) float row_cache[];
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  pdl_wait();
+  pdl_trigger<32>();
+  const int src = rows ? rows[r] : r;
+  float* res = residual + (size_t)src * hidden;
+  float inv_post = 0.0f;
+  if (update) {
+    const T* up = update + (size_t)src * hidden;
+    float sum_sq = 0.0f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float u = to_float(up[i]);
+      row_cache[i] = u;
+      sum_sq = fmaf(u, u, sum_sq);
+    }
+    inv_post = 1.0f / sqrtf(block_sum(sum_sq, scratch) / (float)hidden + eps_post);
+  }
+  const float* ex = extra ? extra + (size_t)src * hidden : nullptr;
+  float sum_sq = 0.0f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float x = res[i];
+    if (update) x += row_cache[i] * inv_post * gain_post[i];
+    if (ex) x += ex[i];
+    if (!rows && (update || ex)) res[i] = x;
+    row_cache[i] = x;
+    sum_sq = fmaf(x, x, sum_sq);
+  }
+  if (!out) return;
+  const float inv_pre = 1.0f / sqrtf(block_sum(sum_sq, scratch) / (float)hidden + eps_pre);
+  T* o = out + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<T>(row_cache[i] * inv_pre * gain_pre[i]);
+}
+
+TS_EXPORT int ts_norm_add_norm(int dtype, float* residual, const void* update, const float* gain_post, float eps_post,
+                               const float* extra, const float* gain_pre, float eps_pre, void* out, const int* rows,
+                               int num_rows, int hidden, cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  if (hidden < 1 || (size_t)hidden * sizeof(float) > 200 * 1024) return TS_ERR_SIZE;
+  if ((update && !gain_post) || (out && !gain_pre)) return TS_ERR_ARGUMENT;
+  int threads = (hidden + 31) / 32 * 32;
+  threads = threads < 64 ? 64 : (threads > 512 ? 512 : threads);
+  const size_t smem = (size_t)hidden * sizeof(float);
+  if (dtype == TS_F32) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(norm_add_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ts_launch(norm_add_norm_kernel<float>, dim3(num_rows), dim3(threads), smem, stream, residual, (const float*)update,
+              gain_post, eps_post, extra, gain_pre, eps_pre, (float*)out, rows, hidden);
+  } else if (dtype == TS_BF16) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(norm_add_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ts_launch(norm_add_norm_kernel<__nv_bfloat16>, dim3(num_rows), dim3(threads), smem, stream, residual,
+              (const __nv_bfloat16*)update, gain_post, eps_post, extra, gain_pre, eps_pre, (__nv_bfloat16*)out, rows, hidden);
+  } else {
+    return TS_ERR_DTYPE;
+  }
+  return ts_launch_status();
+}
+
 // out = act(in): 0 relu^2, 1 gelu (tanh form), 2 silu, 3 tanh.
 __device__ __forceinline__ float plain_activation(float x, int act) {
   if (act == 0) {
@@ -197,6 +272,23 @@ TS_EXPORT int ts_scale_rows(float* data, long long count, float factor, cudaStre
   return ts_launch_status();
 }
 
+// fp32 rows bent into (-cap, cap): x <- cap * tanh(x / cap), in place (a head whose logits are capped).
+__global__ void softcap_rows_kernel(float* __restrict__ data, long long count, float cap) {
+  pdl_wait();
+  pdl_trigger<1>();
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const float inv = 1.0f / cap;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) data[i] = cap * tanhf(data[i] * inv);
+}
+
+TS_EXPORT int ts_softcap_rows(float* data, long long count, float cap, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  if (!(cap > 0.0f)) return TS_ERR_ARGUMENT;
+  long long blocks = (count + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  ts_launch(softcap_rows_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, data, count, cap);
+  return ts_launch_status();
+}
 
 // ---------------------------------------------------------------------------------------
 // norm_pair_mix: out = wa * (a / rms(a) * gain_a) + wb * (b / rms(b) * gain_b), each input normed over the whole

@@ -58,13 +58,20 @@ class DecoderModel:
                 feed_forward = FEED_FORWARDS.get(layer.feed_forward.kind)(layer.feed_forward, spec.hidden_size, dtype, self.device)
                 ff_norm = NORMS.get(layer.feed_forward_norm.kind)(layer.feed_forward_norm, spec.hidden_size, dtype, self.device)
             mixer_norm = NORMS.get(layer.mixer_norm.kind)(layer.mixer_norm, spec.hidden_size, dtype, self.device)
+            behind = {}  # norms behind the sublayers, for blocks that have them
+            for name, norm_spec in (("mixer_output_norm", layer.mixer_output_norm),
+                                    ("feed_forward_output_norm", layer.feed_forward_output_norm)):
+                if norm_spec is not None:
+                    behind[name] = NORMS.get(norm_spec.kind)(norm_spec, spec.hidden_size, dtype, self.device)
             for part, part_prefix in ((mixer_norm, spec.names.mixer_norm), (mixer, spec.names.mixer),
-                                      (ff_norm, spec.names.feed_forward_norm), (feed_forward, spec.names.feed_forward)):
+                                      (behind.get("mixer_output_norm"), spec.names.mixer_output_norm),
+                                      (ff_norm, spec.names.feed_forward_norm), (feed_forward, spec.names.feed_forward),
+                                      (behind.get("feed_forward_output_norm"), spec.names.feed_forward_output_norm)):
                 if part is None:
                     continue
                 self.parts_list.append(part)
                 self._part_prefix.append(prefix + part_prefix)
-            self.blocks.append(BLOCKS.get(layer.block)(mixer, feed_forward, mixer_norm, ff_norm, **dict(layer.block_params)))
+            self.blocks.append(BLOCKS.get(layer.block)(mixer, feed_forward, mixer_norm, ff_norm, **behind, **dict(layer.block_params)))
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, spec.hidden_size, dtype, self.device)
         self.parts_list.append(self.final_norm)
         self._part_prefix.append(spec.names.final_norm)
@@ -163,7 +170,8 @@ class DecoderModel:
         mixers = max(declared(block.mixer) for block in self.blocks)
         feed_forwards = max(declared(block.feed_forward) if block.feed_forward is not None else 0 for block in self.blocks)
         around = declared(self.embedding) + declared(self.head)
-        return 4 * self.hidden_size + itemsize * (self.hidden_size + mixers + feed_forwards + around)
+        kept = 4 * self.hidden_size if any(run.readds_embedding for run in self.spec.order) else 0  # the embedding's output, fp32
+        return 4 * self.hidden_size + kept + itemsize * (self.hidden_size + mixers + feed_forwards + around)
 
     @property
     def graph_safe(self) -> bool:
@@ -186,23 +194,30 @@ class DecoderModel:
         n = batch.num_tokens
         residual = ctx.buffer("model.residual", (n, self.hidden_size), torch.float32)
         self.embedding.forward(residual, ctx)
+        embedded = None
+        if any(run.readds_embedding for run in self.spec.order):  # kept apart: the stream itself moves on
+            embedded = ctx.buffer("model.embedded", (n, self.hidden_size), torch.float32)
+            self.embedding.forward(embedded, ctx)
         pending = None
         for run_index, run in enumerate(self.spec.order):
             ctx.run_index = run_index
             block = self.blocks[run.layer]
-            if run.shift is None:
+            if run.shift is None and not run.readds_embedding:
                 pending = block.forward(residual, pending, ctx, storage.run_caches[run_index])
                 continue
-            shift = self.stream_shifts.row(run.shift)
-            if getattr(block, "takes_shift", False):  # its first norm adds the shift with the pending updates
-                pending = block.forward(residual, pending, ctx, storage.run_caches[run_index], shift=shift)
+            extras = {}
+            if run.shift is not None:
+                extras["shift"] = self.stream_shifts.row(run.shift)
+            if run.readds_embedding:
+                extras["rows_added"] = embedded
+            takes = (("shift" not in extras or getattr(block, "takes_shift", False))
+                     and ("rows_added" not in extras or getattr(block, "takes_rows", False)))
+            if takes:  # its first norm adds them with the pending updates
+                pending = block.forward(residual, pending, ctx, storage.run_caches[run_index], **extras)
             else:
-                from ..ops import kernels
+                from ..parts.base import settle_pending
 
-                from ..parts.base import pending_updates
-
-                updates, mult = pending_updates(pending)
-                kernels.stream_norm(residual, updates, shift, None, None, num_rows=n, dtype=self.dtype, mult=mult)
+                settle_pending(residual, pending, n, self.dtype, **extras)
                 pending = block.forward(residual, None, ctx, storage.run_caches[run_index])
         rows = batch.num_logit_rows
         if rows == 0:

@@ -191,8 +191,10 @@ def head_norm_rope_write(qkv: torch.Tensor, q_gain: torch.Tensor | None, k_gain:
                          positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
                          k_pages: torch.Tensor | None, v_pages: torch.Tensor | None, num_tokens: int, num_heads: int,
                          num_kv_heads: int, dim: int, vdim: int, inv_freq: torch.Tensor | None, rotary_dim: int,
-                         interleaved: bool, write_kv: bool, status: torch.Tensor | None = None) -> None:
-    """RMS norm per head of q and k (gains of ``dim`` floats shared by the heads, or ``None``), rotation of the first
+                         interleaved: bool, write_kv: bool, status: torch.Tensor | None = None,
+                         bias: torch.Tensor | None = None) -> None:
+    """The projection's ``bias`` (float32, as wide as a row's heads, or ``None``), RMS norm per head of q and k (gains of
+    ``dim`` floats shared by the heads, or ``None``), rotation of the first
     ``rotary_dim`` elements (pairs ``(2i, 2i + 1)`` when ``interleaved``, else ``(i, i + rotary_dim / 2)``), and the
     append of keys (``dim`` wide) and values (``vdim`` wide) to their pages; all in fp32, rounded once.
 
@@ -221,10 +223,14 @@ def head_norm_rope_write(qkv: torch.Tensor, q_gain: torch.Tensor | None, k_gain:
         _need(inv_freq, torch.float32, "inv_freq")
         if inv_freq.numel() * 2 != rotary_dim:
             raise KernelError("head_norm_rope_write: inv_freq must hold rotary_dim / 2 values")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
+        if bias.numel() != (num_heads + num_kv_heads) * dim + num_kv_heads * vdim or not bias.is_contiguous():
+            raise KernelError("head_norm_rope_write: the bias must be as wide as a row's heads")
     fn = _fn("layer_ops", "ts_head_norm_rope_write",
-             [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+             [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
               c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
-    _check(fn(dtype_code(qkv.dtype), _ptr(qkv), qkv.stride(0), _ptr(q_gain), _ptr(k_gain), float(eps), _ptr(positions),
+    _check(fn(dtype_code(qkv.dtype), _ptr(qkv), qkv.stride(0), _ptr(bias), _ptr(q_gain), _ptr(k_gain), float(eps), _ptr(positions),
               _ptr(seq_of_token), _ptr(block_table), block_table.stride(0), _ptr(k_pages), _ptr(v_pages), page_size,
               num_tokens, num_heads, num_kv_heads, dim, vdim, _ptr(inv_freq), int(rotary_dim), 1 if interleaved else 0,
               1 if write_kv else 0, _ptr(status), _stream()), "head_norm_rope_write")
@@ -263,10 +269,12 @@ def paged_attention_capped(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Te
                            block_table: torch.Tensor, seq_of_token: torch.Tensor, positions: torch.Tensor,
                            num_tokens: int, num_heads: int, num_kv_heads: int, head_dim: int, v_dim: int,
                            window: int | None, scale: float, softcap: float = 0.0, sink: bool = False,
-                           status: torch.Tensor | None = None) -> None:
+                           status: torch.Tensor | None = None, sink_values: torch.Tensor | None = None) -> None:
     """:func:`paged_attention_generic` with every option: value rows of ``v_dim`` elements, scores capped as
-    ``softcap * tanh(score / softcap)`` (0: uncapped), and a ``sink`` (one added to the softmax's denominator, as if
-    one more key scored 0 and had no value). ``out`` is ``[tokens, >= num_heads * v_dim]``."""
+    ``softcap * tanh(score / softcap)`` (0: uncapped), and a ``sink`` (one more term in the softmax's denominator, as if
+    one more key had no value; it scores 0, or ``sink_values[head]`` (float32, one a query head), taken as it is).
+    ``out`` is ``[tokens, >= num_heads * v_dim]``."""
+    _need_sink(sink, sink_values, num_heads)
     _need(q, None, "q"); _need(out, q.dtype, "out"); _need(k_pages, q.dtype, "k_pages"); _need(v_pages, q.dtype, "v_pages")
     _need(block_table, torch.int32, "block_table"); _need(seq_of_token, torch.int32, "seq_of_token"); _need(positions, torch.int32, "positions")
     if (not k_pages.is_contiguous() or not v_pages.is_contiguous() or tuple(k_pages.shape[2:]) != (num_kv_heads, head_dim)
@@ -276,11 +284,19 @@ def paged_attention_capped(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Te
         raise KernelError("paged_attention: q or out is narrower than its heads")
     fn = _fn("attention_generic", "ts_paged_attention_capped",
              [c_int, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p])
+              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p, c_void_p])
     _check(fn(dtype_code(q.dtype), _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages),
               _ptr(block_table), block_table.stride(0), _ptr(seq_of_token), _ptr(positions), num_tokens,
               k_pages.shape[1], num_heads, num_kv_heads, head_dim, v_dim, int(window or 0), float(scale), float(softcap),
-              1 if sink else 0, _ptr(status), _stream()), "paged_attention_capped")
+              1 if sink else 0, _ptr(sink_values), _ptr(status), _stream()), "paged_attention_capped")
+
+
+def _need_sink(sink: bool, sink_values: torch.Tensor | None, num_heads: int) -> None:
+    if sink_values is None:
+        return
+    _need(sink_values, torch.float32, "sink_values")
+    if not sink or sink_values.numel() != num_heads or not sink_values.is_contiguous():
+        raise KernelError("attention: sink_values must hold one float per query head, and go with a sink")
 
 
 def paged_attention_capped_mma_takes(dtype: torch.dtype, dim: int, vdim: int, scale: float = 1.0) -> bool:
@@ -293,7 +309,7 @@ def paged_attention_capped_mma(q: torch.Tensor, out: torch.Tensor, k_pages: torc
                                block_table: torch.Tensor, query_start: torch.Tensor, context_lens: torch.Tensor,
                                num_tokens: int, num_seqs: int, num_heads: int, num_kv_heads: int, head_dim: int, v_dim: int,
                                window: int | None, scale: float, softcap: float = 0.0, sink: bool = False,
-                               status: torch.Tensor | None = None) -> None:
+                               status: torch.Tensor | None = None, sink_values: torch.Tensor | None = None) -> None:
     """:func:`paged_attention_capped` for bfloat16 steps with portions of prompts, on tensor cores: tiles of 64
     positions of a request, found through ``query_start`` and ``context_lens`` (``[seqs + 1]`` and ``[seqs]``)."""
     for name, tensor in (("q", q), ("out", out), ("k_pages", k_pages), ("v_pages", v_pages)):
@@ -308,11 +324,12 @@ def paged_attention_capped_mma(q: torch.Tensor, out: torch.Tensor, k_pages: torc
         raise KernelError("paged_attention_capped_mma: fewer requests than asked for")
     fn = _fn("attention_capped_mma", "ts_paged_attention_capped_mma",
              [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p])
+              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p, c_void_p, c_void_p])
+    _need_sink(sink, sink_values, num_heads)
     _check(fn(_ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
               block_table.stride(0), _ptr(query_start), _ptr(context_lens), num_tokens, num_seqs, k_pages.shape[1],
               num_heads, num_kv_heads, head_dim, v_dim, int(window or 0), float(scale), float(softcap), 1 if sink else 0,
-              _ptr(status), _stream()), "paged_attention_capped_mma")
+              _ptr(sink_values), _ptr(status), _stream()), "paged_attention_capped_mma")
 
 
 # ---------------------------------------------------------------------------------------
@@ -427,6 +444,48 @@ def norm_add(residual: torch.Tensor, update: torch.Tensor | None, gain: torch.Te
     fn = _fn("stream_ops", "ts_norm_add", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p])
     _check(fn(dtype_code(kind), _ptr(residual), _ptr(update), _ptr(gain), _ptr(copy), num_rows, hidden, float(eps),
               float(mult), _stream()), "norm_add")
+
+
+def norm_add_norm(residual: torch.Tensor, update: torch.Tensor | None, gain_post: torch.Tensor | None, eps_post: float,
+                  extra: torch.Tensor | None, gain_pre: torch.Tensor | None, eps_pre: float, out: torch.Tensor | None,
+                  num_rows: int, dtype: torch.dtype | None = None, rows: torch.Tensor | None = None) -> None:
+    """``residual += rms_norm(update) * gain_post`` (the norm taken over the update alone), ``residual += extra`` (float32
+    rows), ``out = rms_norm(residual) * gain_pre``; every part optional, all in float32, ``out`` rounded once. With
+    ``rows`` (int32) only the listed rows are worked and ``residual`` is not written. ``dtype`` names the activation
+    type when neither ``update`` nor ``out`` is given."""
+    _need(residual, torch.float32, "residual")
+    hidden = residual.shape[-1]
+    kind = update.dtype if update is not None else (out.dtype if out is not None else (dtype or torch.float32))
+    if not residual.is_contiguous():
+        raise KernelError("norm_add_norm: the residual must be contiguous")
+    if update is not None:
+        _need(update, kind, "update"); _need(gain_post, torch.float32, "gain_post")
+        if not update.is_contiguous() or update.shape[-1] != hidden or gain_post.numel() != hidden:
+            raise KernelError("norm_add_norm: the update and its gain must be as wide as the residual")
+    if extra is not None:
+        _need(extra, torch.float32, "extra")
+        if not extra.is_contiguous() or extra.shape[-1] != hidden:
+            raise KernelError("norm_add_norm: the added rows must be contiguous float32 rows as wide as the residual")
+    if out is not None:
+        _need(out, kind, "out"); _need(gain_pre, torch.float32, "gain_pre")
+        if not out.is_contiguous() or out.shape[-1] != hidden or gain_pre.numel() != hidden or out.shape[0] < num_rows:
+            raise KernelError("norm_add_norm: out and its gain must be as wide as the residual")
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    fn = _fn("stream_ops", "ts_norm_add_norm", [c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_float, c_void_p,
+                                                c_void_p, c_int, c_int, c_void_p])
+    _check(fn(dtype_code(kind), _ptr(residual), _ptr(update), _ptr(gain_post), float(eps_post), _ptr(extra), _ptr(gain_pre),
+              float(eps_pre), _ptr(out), _ptr(rows), int(num_rows), hidden, _stream()), "norm_add_norm")
+
+
+def softcap_rows(data: torch.Tensor, cap: float, num_rows: int | None = None) -> None:
+    """``data[:num_rows] = cap * tanh(data[:num_rows] / cap)`` in place; float32 rows."""
+    _need(data, torch.float32, "data")
+    if not data.is_contiguous():
+        raise KernelError("softcap_rows: data must be contiguous")
+    rows = data.shape[0] if num_rows is None else num_rows
+    fn = _fn("stream_ops", "ts_softcap_rows", [c_void_p, c_longlong, c_float, c_void_p])
+    _check(fn(_ptr(data), rows * (data.numel() // max(data.shape[0], 1)), float(cap), _stream()), "softcap_rows")
 
 
 def activation(x: torch.Tensor, out: torch.Tensor, name: str, num_rows: int | None = None) -> None:
@@ -679,18 +738,25 @@ def latent_prepare(q: torch.Tensor, down: torch.Tensor | None, norm_weight: torc
               _stream()), "latent_prepare")
 
 
-def head_linear(x: torch.Tensor, in_head: int, weight: torch.Tensor, out: torch.Tensor, out_head: int, num_rows: int) -> None:
-    """``out[t, h * out_head + n] = sum_k x[t, h * in_head + k] * weight[h, n, k]`` for every head ``h`` in one launch."""
+def head_linear(x: torch.Tensor, in_head: int, weight: torch.Tensor, out: torch.Tensor, out_head: int, num_rows: int,
+                gate: torch.Tensor | None = None) -> None:
+    """``out[t, h * out_head + n] = sum_k x[t, h * in_head + k] * weight[h, n, k]`` for every head ``h`` in one launch;
+    with ``gate`` (``[rows, >= heads]``, the same type) a head's outputs are multiplied by ``sigmoid(gate[t, h])``."""
     _need(x, None, "x"); _need(weight, x.dtype, "weight"); _need(out, x.dtype, "out")
     heads, n, k = weight.shape
+    if gate is not None:
+        _need(gate, x.dtype, "gate")
+        if gate.dim() != 2 or gate.shape[0] < num_rows or gate.shape[1] < heads:
+            raise KernelError("head_linear: the gate holds one number per row and head")
     if not weight.is_contiguous() or x.shape[1] < (heads - 1) * in_head + k or out.shape[1] < (heads - 1) * out_head + n:
         raise KernelError("head_linear: the rows are narrower than their heads")
     if x.shape[0] < num_rows or out.shape[0] < num_rows:
         raise KernelError("head_linear: fewer rows than asked for")
     fn = _fn("latent_attention", "ts_head_linear",
-             [c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p])
+             [c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p,
+              c_longlong, c_void_p])
     _check(fn(dtype_code(x.dtype), _ptr(x), x.stride(0), int(in_head), _ptr(weight), _ptr(out), out.stride(0), int(out_head),
-              num_rows, heads, n, k, _stream()), "head_linear")
+              num_rows, heads, n, k, _ptr(gate), 0 if gate is None else gate.stride(0), _stream()), "head_linear")
 
 
 def latent_attention(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, block_table: torch.Tensor,
@@ -882,36 +948,52 @@ def chosen_decay_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, bonus: 
 
 
 def moe_route(x: torch.Tensor, router: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, num_tokens: int, top: int,
-              groups: int = 1, keep: int = 1) -> None:
-    """Per token the ``top`` experts with the largest softmax score among the ``keep`` best of ``groups`` groups
-    (``chosen`` int32 ``[tokens, top]``) and their scores over their sum (``weights`` float32)."""
+              groups: int = 1, keep: int = 1, score: str = "softmax", renormalize: bool = True) -> None:
+    """Per token the ``top`` experts with the largest score among the ``keep`` best of ``groups`` groups (``chosen`` int32
+    ``[tokens, top]``) and their weights (float32): the scores are a softmax over all experts or, with ``score="sigmoid"``,
+    each expert's own sigmoid; the weights are the chosen scores over their sum, or as they are without ``renormalize``."""
+    if score not in ("softmax", "sigmoid"):
+        raise KernelError(f"moe_route: scores are a softmax or sigmoids, not {score!r}")
+    mode = (1 if score == "sigmoid" else 0) | (0 if renormalize else 2)
     _need(x, None, "x"); _need(router, torch.float32, "router"); _need(chosen, torch.int32, "chosen"); _need(weights, torch.float32, "weights")
     experts, width = router.shape
     if not router.is_contiguous() or x.shape[1] != width or chosen.numel() < num_tokens * top or weights.numel() < num_tokens * top:
         raise KernelError("moe_route: shapes do not agree")
-    fn = _fn("moe_ops", "ts_moe_route", [c_int, c_void_p, c_longlong, c_void_p] + [c_int] * 6 + [c_void_p] * 3)
+    fn = _fn("moe_ops", "ts_moe_route", [c_int, c_void_p, c_longlong, c_void_p] + [c_int] * 7 + [c_void_p] * 3)
     _check(fn(dtype_code(x.dtype), _ptr(x), x.stride(0), _ptr(router), num_tokens, width, experts, int(top), int(groups),
-              int(keep), _ptr(chosen), _ptr(weights), _stream()), "moe_route")
+              int(keep), mode, _ptr(chosen), _ptr(weights), _stream()), "moe_route")
+
+
+def _need_pair_weights(in_weights: torch.Tensor | None, pairs: int, name: str) -> None:
+    if in_weights is not None:
+        _need(in_weights, torch.float32, "in_weights")
+        if in_weights.numel() < pairs or not in_weights.is_contiguous():
+            raise KernelError(f"{name}: in_weights holds one float per (token, expert) pair")
 
 
 def moe_pair_gate_up(x: torch.Tensor, gate_up: torch.Tensor, chosen: torch.Tensor, hidden: torch.Tensor, num_tokens: int,
-                     top: int, activation: str) -> None:
-    """``hidden[t * top + k] = act(gate_e x_t) * (up_e x_t)`` for ``e = chosen[t, k]``; ``gate_up`` is ``[experts, 2 * ff, width]``."""
+                     top: int, activation: str, in_weights: torch.Tensor | None = None) -> None:
+    """``hidden[t * top + k] = act(gate_e x_t) * (up_e x_t)`` for ``e = chosen[t, k]``; ``gate_up`` is ``[experts, 2 * ff, width]``.
+    With ``in_weights`` (float32 ``[tokens, top]``) the expert reads ``in_weights[t, k] * x_t``."""
+    _need_pair_weights(in_weights, num_tokens * top, "moe_pair_gate_up")
     _need(x, None, "x"); _need(gate_up, x.dtype, "gate_up"); _need(hidden, x.dtype, "hidden"); _need(chosen, torch.int32, "chosen")
     experts, twice, width = gate_up.shape
     ff = twice // 2
     if not gate_up.is_contiguous() or not hidden.is_contiguous() or x.shape[1] != width or hidden.shape[1] != ff or hidden.shape[0] < num_tokens * top:
         raise KernelError("moe_pair_gate_up: shapes do not agree")
-    fn = _fn("moe_ops", "ts_moe_pair_gate_up", [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p] + [c_int] * 5 + [c_void_p])
-    _check(fn(dtype_code(x.dtype), _ptr(x), x.stride(0), _ptr(gate_up), _ptr(chosen), _ptr(hidden), num_tokens, width, ff,
+    fn = _fn("moe_ops", "ts_moe_pair_gate_up", [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 5 + [c_void_p])
+    _check(fn(dtype_code(x.dtype), _ptr(x), x.stride(0), _ptr(gate_up), _ptr(chosen), _ptr(in_weights), _ptr(hidden), num_tokens, width, ff,
               int(top), ACTIVATION_CODES[activation], _stream()), "moe_pair_gate_up")
 
 
-def moe_pair_down(hidden: torch.Tensor, down: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor,
+def moe_pair_down(hidden: torch.Tensor, down: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor | None,
                   addend: torch.Tensor | None, out: torch.Tensor, num_tokens: int, top: int) -> None:
-    """``out[t] = sum_k weights[t, k] * (down_e hidden[t * top + k]) (+ addend[t])``; ``down`` is ``[experts, width, ff]``."""
+    """``out[t] = sum_k weights[t, k] * (down_e hidden[t * top + k]) (+ addend[t])``; ``down`` is ``[experts, width, ff]``;
+    without ``weights`` every term counts once."""
     _need(hidden, None, "hidden"); _need(down, hidden.dtype, "down"); _need(out, hidden.dtype, "out")
-    _need(chosen, torch.int32, "chosen"); _need(weights, torch.float32, "weights")
+    _need(chosen, torch.int32, "chosen")
+    if weights is not None:
+        _need(weights, torch.float32, "weights")
     experts, width, ff = down.shape
     if addend is not None:
         _need(addend, hidden.dtype, "addend")
@@ -925,21 +1007,23 @@ def moe_pair_down(hidden: torch.Tensor, down: torch.Tensor, chosen: torch.Tensor
 
 
 def moe_expert_rows(gated: bool, rows_in: torch.Tensor, weights: torch.Tensor, counters: torch.Tensor, pair_of_row: torch.Tensor,
-                    out: torch.Tensor, top: int, activation: str = "silu") -> None:
+                    out: torch.Tensor, top: int, activation: str = "silu", in_weights: torch.Tensor | None = None) -> None:
     """Every expert's rows (in the order :func:`moe_sort` made) times that expert's matrix, the weights streamed once for up
     to eight rows at a time. ``gated``: ``rows_in`` is the step's inputs ``[tokens, width]`` (gathered through ``pair_of_row``),
     ``weights`` ``[experts, 2 * ff, width]`` and ``out[row] = act(gate x) * (up x)``; else ``rows_in`` is ``[pairs, ff]`` in
-    expert order, ``weights`` ``[experts, width, ff]`` and ``out[row] = W rows_in[row]``. ``out`` has one row a pair."""
+    expert order, ``weights`` ``[experts, width, ff]`` and ``out[row] = W rows_in[row]``. ``out`` has one row a pair.
+    With ``in_weights`` (float32, one a pair; gated only) the expert reads its token's row times the pair's weight."""
+    _need_pair_weights(in_weights if gated else None, out.shape[0], "moe_expert_rows")
     _need(rows_in, None, "rows_in"); _need(weights, rows_in.dtype, "weights"); _need(out, rows_in.dtype, "out")
     _need(counters, torch.int32, "counters"); _need(pair_of_row, torch.int32, "pair_of_row")
     experts, n_rows, k = weights.shape
     n_out = n_rows // 2 if gated else n_rows
     if not weights.is_contiguous() or not out.is_contiguous() or rows_in.shape[1] != k or out.shape[1] != n_out or counters.numel() < 2 * experts + 1:
         raise KernelError("moe_expert_rows: shapes do not agree")
-    fn = _fn("moe_ops", "ts_moe_expert_rows", [c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 6 + [c_void_p])
+    fn = _fn("moe_ops", "ts_moe_expert_rows", [c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 6 + [c_void_p, c_void_p])
     _check(fn(dtype_code(rows_in.dtype), 1 if gated else 0, _ptr(rows_in), rows_in.stride(0), _ptr(weights), _ptr(counters),
-              _ptr(pair_of_row), _ptr(out), k, n_out, int(top), experts, out.shape[0], ACTIVATION_CODES[activation], _stream()),
-           "moe_expert_rows")
+              _ptr(pair_of_row), _ptr(out), k, n_out, int(top), experts, out.shape[0], ACTIVATION_CODES[activation],
+              _ptr(in_weights if gated else None), _stream()), "moe_expert_rows")
 
 
 MOE_EXPERT_ROWS_SMEM = 200 * 1024
@@ -960,20 +1044,25 @@ def moe_sort(chosen: torch.Tensor, num_pairs: int, experts: int, counters: torch
            launches=1 if num_pairs <= 4096 and experts <= 2048 else 3)  # one block sorts a few pairs
 
 
-def moe_gather(x: torch.Tensor, pair_of_row: torch.Tensor, rows: torch.Tensor, num_pairs: int, top: int) -> None:
-    """``rows[r] = x[pair_of_row[r] // top]``."""
+def moe_gather(x: torch.Tensor, pair_of_row: torch.Tensor, rows: torch.Tensor, num_pairs: int, top: int,
+               in_weights: torch.Tensor | None = None) -> None:
+    """``rows[r] = x[pair_of_row[r] // top]``, times ``in_weights[pair_of_row[r]]`` if given (fp32 product, rounded once)."""
+    _need_pair_weights(in_weights, num_pairs, "moe_gather")
     _need(x, None, "x"); _need(rows, x.dtype, "rows"); _need(pair_of_row, torch.int32, "pair_of_row")
     if not rows.is_contiguous() or rows.shape[1] != x.shape[1] or rows.shape[0] < num_pairs:
         raise KernelError("moe_gather: rows must be contiguous [pairs, width]")
-    fn = _fn("moe_ops", "ts_moe_gather", [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    fn = _fn("moe_ops", "ts_moe_gather", [c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(fn(dtype_code(x.dtype), _ptr(x), x.stride(0), _ptr(pair_of_row), _ptr(rows), num_pairs, x.shape[1], int(top),
-              _stream()), "moe_gather")
+              _ptr(in_weights), _stream()), "moe_gather")
 
 
-def moe_combine(rows: torch.Tensor, place: torch.Tensor, weights: torch.Tensor, addend: torch.Tensor | None, out: torch.Tensor,
+def moe_combine(rows: torch.Tensor, place: torch.Tensor, weights: torch.Tensor | None, addend: torch.Tensor | None, out: torch.Tensor,
                 num_tokens: int, top: int) -> None:
-    """``out[t] = sum_k weights[t, k] * rows[place[t * top + k]] (+ addend[t])`` in fp32, rounded once."""
-    _need(rows, None, "rows"); _need(out, rows.dtype, "out"); _need(place, torch.int32, "place"); _need(weights, torch.float32, "weights")
+    """``out[t] = sum_k weights[t, k] * rows[place[t * top + k]] (+ addend[t])`` in fp32, rounded once; without ``weights``
+    every row counts once."""
+    _need(rows, None, "rows"); _need(out, rows.dtype, "out"); _need(place, torch.int32, "place")
+    if weights is not None:
+        _need(weights, torch.float32, "weights")
     width = out.shape[1]
     if addend is not None:
         _need(addend, rows.dtype, "addend")

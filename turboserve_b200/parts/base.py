@@ -23,7 +23,8 @@ Constructor signatures
     feed-forward   ``cls(spec, hidden_size, dtype, device)``
     norm           ``cls(spec, hidden_size, dtype, device)``
     position       ``cls(spec, device)``
-    block          ``cls(mixer, feed_forward, mixer_norm, feed_forward_norm)``
+    block          ``cls(mixer, feed_forward, mixer_norm, feed_forward_norm, **block_params)``; a layer that also
+                   names norms behind its sublayers hands them on as ``mixer_output_norm=``, ``feed_forward_output_norm=``
     embedding      ``cls(spec, hidden_size, vocab_size, dtype, device)``
     stream shifts  ``cls(spec, hidden_size, dtype, device)``
     head           ``cls(spec, hidden_size, vocab_size, dtype, device, tied=False)``
@@ -137,10 +138,39 @@ class ScaledUpdates(tuple):
         return self
 
 
+class NormedUpdate:
+    """An update a block leaves pending that enters the stream through a norm of its own:
+    ``stream += rms_norm(update) * gain`` (statistics over the update alone, ``eps`` inside the root).
+
+    Whoever takes the pending update next (a norm's ``forward`` or ``forward_rows``, or :func:`settle_pending`) does
+    this sum in the same kernel as its own work."""
+
+    def __init__(self, update: torch.Tensor, gain: torch.Tensor, eps: float) -> None:
+        self.update, self.gain, self.eps = update, gain, float(eps)
+
+
+def settle_pending(residual: torch.Tensor, pending, num_rows: int, dtype: torch.dtype, shift: torch.Tensor | None = None,
+                   rows_added: torch.Tensor | None = None) -> None:
+    """Add what a block left pending into the float32 stream now, with a vector ``shift`` for every row and a matrix
+    ``rows_added`` (float32, a row a token), if given; nothing is normed for the next sublayer."""
+    from ..ops import kernels
+
+    if isinstance(pending, NormedUpdate):
+        kernels.norm_add_norm(residual, pending.update, pending.gain, pending.eps, rows_added, None, 0.0, None, num_rows, dtype)
+        pending, rows_added = None, None
+    elif rows_added is not None:
+        kernels.norm_add_norm(residual, None, None, 0.0, rows_added, None, 0.0, None, num_rows, dtype)
+    updates, mult = pending_updates(pending)
+    if updates or shift is not None:
+        kernels.stream_norm(residual, updates, shift, None, None, num_rows=num_rows, dtype=dtype, mult=mult)
+
+
 def pending_updates(pending) -> tuple[tuple, float]:
     """What a block left pending as ``(updates, mult)``, whatever form it was handed on in."""
     if pending is None:
         return (), 1.0
+    if isinstance(pending, NormedUpdate):
+        raise TypeError("an update that enters the stream through its own norm is taken by a norm or by settle_pending")
     items = pending if isinstance(pending, (tuple, list)) else (pending,)
     return tuple(p for p in items if p is not None), float(getattr(pending, "mult", 1.0))
 

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import FeedForward, Mixer, Norm, ScaledUpdates, pending_updates, register_block
+from .base import FeedForward, Mixer, Norm, NormedUpdate, ScaledUpdates, pending_updates, register_block, settle_pending
 
 
 class PreNormBlock:
@@ -103,8 +103,7 @@ class OutputNormBlock:
 
         n, hidden = ctx.batch.num_tokens, residual.shape[-1]
         if pending is not None:  # what a block of another kind before this one left to be added
-            updates, mult = pending_updates(pending)
-            kernels.stream_norm(residual, updates, None, None, None, num_rows=n, dtype=ctx.dtype, mult=mult)
+            settle_pending(residual, pending, n, ctx.dtype)
             ctx.stream_copy = None
         if ctx.dtype == torch.float32:
             x = copy = None
@@ -123,6 +122,51 @@ class OutputNormBlock:
         return None
 
 
+class BothSidesNormBlock:
+    """Norms before and behind each sublayer: ``h += post1(mixer(pre1(h))); h += post2(feed_forward(pre2(h)))``.
+
+    What stands between two sublayers is one kernel: the norm behind the sublayer that ran (statistics over its output
+    alone), the sum into the fp32 stream, and the norm before the sublayer that runs next. The feed-forward's output is
+    therefore left pending with its norm (:class:`~turboserve_b200.parts.base.NormedUpdate`) and enters the stream in
+    the next block's first kernel, or in the final norm's. ``rows_added`` is a float32 matrix, a row a token, added to
+    the stream right before the layer (a repeated stretch of layers adds the embedding's output before each pass but
+    the first). A layer without a feed-forward has one sublayer.
+    """
+
+    takes_shift = True
+    takes_rows = True
+
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward | None, mixer_norm: Norm, feed_forward_norm: Norm | None,
+                 mixer_output_norm: Norm | None = None, feed_forward_output_norm: Norm | None = None) -> None:
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.mixer_norm = mixer_norm
+        self.feed_forward_norm = feed_forward_norm
+        self.mixer_output_norm = mixer_output_norm
+        self.feed_forward_output_norm = feed_forward_output_norm
+        if mixer_output_norm is None or not hasattr(mixer_output_norm, "normed"):
+            raise ValueError("this block needs a norm behind its mixer that can travel with a pending update (normed)")
+        if (feed_forward is None) != (feed_forward_norm is None) or (feed_forward is None) != (feed_forward_output_norm is None):
+            raise ValueError("a feed-forward and its two norms go together")
+        if feed_forward_output_norm is not None and not hasattr(feed_forward_output_norm, "normed"):
+            raise ValueError("this block needs a norm behind its feed-forward that can travel with a pending update (normed)")
+
+    def forward(self, residual: torch.Tensor, pending, ctx, cache, shift: torch.Tensor | None = None,
+                rows_added: torch.Tensor | None = None):
+        n, hidden = ctx.batch.num_tokens, residual.shape[-1]
+        normed = ctx.buffer("block.normed", (n, hidden))
+        if rows_added is None:
+            self.mixer_norm.forward(residual, pending, normed, ctx, shift=shift)
+        else:
+            self.mixer_norm.forward(residual, pending, normed, ctx, shift=shift, rows_added=rows_added)
+        mixed = self.mixer_output_norm.normed(self.mixer.forward(normed, ctx, cache))
+        if self.feed_forward is None:
+            return mixed
+        self.feed_forward_norm.forward(residual, mixed, normed, ctx)
+        return self.feed_forward_output_norm.normed(self.feed_forward.forward(normed, ctx))
+
+
 register_block("pre_norm", PreNormBlock)
+register_block("both_sides_norm", BothSidesNormBlock)
 register_block("output_norm", OutputNormBlock)
 register_block("parallel", ParallelBlock)

@@ -21,14 +21,21 @@ product (bfloat16 operands, float32 accumulation and result), a kernel takes the
 float32 and rounds the weights to bfloat16, and a second product sums the latents.
 
 The rotation acts on pairs ``(i, i + rot_dim / 2)`` with frequencies from ``rot`` (``base``, ``dims``, optional
-``scaling``: see :func:`~turboserve_b200.parts.rope.scaled_rotary_frequencies`); ``scale`` is used as given.
+``scaling``: see :func:`~turboserve_b200.parts.rope.rotary_frequencies`); ``scale`` is used as given. With
+``rot.interleaved`` the checkpoint pairs neighbours ``(2i, 2i + 1)`` instead: the rows of ``Wq`` and ``Wdkv`` that make
+the rotated parts are put in the other order once, when the weights are bound (a score is a sum over the rotated
+elements, so the order they are kept in is free as long as queries and keys share it).
+
+With ``gate`` a head's output is multiplied by ``sigmoid(Wg h)_head`` before the output projection (``Wg`` has one row
+a head and reads the mixer's input; its rows ride in the fused projection, the sigmoid and the product are fp32 in
+the kernel that applies ``Wuv``).
 
 With ``shares_cache`` the mixer has no ``Wdkv`` and attends over the rows another run writes, with its own
 queries, ``Wuk``, ``Wuv`` and window; ``cache_window`` is then the window the shared pages are kept for (the
 largest of the runs that read them; ``None`` keeps everything).
 
 Sizes and constants are parameters: ``heads``, ``dim``, ``rot_dim``, ``vdim``, ``kv_rank``, ``scale``, ``window``,
-``cache_window``, ``eps``, ``rot``; ``names`` maps the roles ``q dkv dkv_norm uk uv o`` to the checkpoint's names.
+``cache_window``, ``eps``, ``rot``, ``gate``; ``names`` maps the roles ``q dkv dkv_norm uk uv o g`` to the checkpoint's names.
 """
 
 from __future__ import annotations
@@ -39,7 +46,7 @@ from ..config.model_spec import PartSpec
 from ..ops import kernels
 from ..ops.linear import linear
 from .base import Mixer, PagedKVNeed, ParamSpec, register_mixer
-from .rope import scaled_rotary_frequencies
+from .rope import rotary_frequencies
 
 PORTION_MIN = 32
 """Tokens a request brings to a step from which its attention is worked as matrix products (bfloat16, windowed)."""
@@ -56,7 +63,7 @@ def matrix_product(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = 
 
 
 DEFAULT_NAMES = {"q": "q_proj.weight", "dkv": "kv_down_proj.weight", "dkv_norm": "kv_norm.weight",
-                 "uk": "k_up_proj.weight", "uv": "v_up_proj.weight", "o": "o_proj.weight"}
+                 "uk": "k_up_proj.weight", "uv": "v_up_proj.weight", "o": "o_proj.weight", "g": "gate_proj.weight"}
 _UNSET = object()
 
 
@@ -85,14 +92,17 @@ class LatentAttention(Mixer):
         if self.rot_dim % 2 or self.rot_dim < 0 or (self.rot_dim and int(rot.get("dims", self.rot_dim)) != self.rot_dim):
             raise ValueError("rot_dim must be even and the rotation must cover all of it")
         if self.rot_dim:
-            freq, self.amplitude = scaled_rotary_frequencies(self.rot_dim, float(rot["base"]), rot.get("scaling"))
+            freq, self.amplitude = rotary_frequencies(self.rot_dim, float(rot["base"]), rot.get("scaling"))
             self.inv_freq = freq.to(device)
         else:
             self.inv_freq, self.amplitude = torch.zeros(0, dtype=torch.float32, device=device), 1.0
         self.q_head = self.dim + self.rot_dim
         self.q_width = self.heads * self.q_head
         self.row = self.rank + self.rot_dim
-        self.proj_width = self.q_width + (0 if self.shares_cache else self.row)
+        self.interleaved = bool(rot.get("interleaved", False))
+        self.gated = bool(spec.get("gate", False))
+        self.gate_first = self.q_width + (0 if self.shares_cache else self.row)
+        self.proj_width = self.gate_first + (self.heads if self.gated else 0)
         for name in ("proj", "norm_w", "uk_t", "uv", "out_w"):
             setattr(self, name, None)
 
@@ -108,17 +118,30 @@ class LatentAttention(Mixer):
         specs = [ParamSpec(n["q"], (self.q_width, h))]
         if not self.shares_cache:
             specs += [ParamSpec(n["dkv"], (self.row, h)), ParamSpec(n["dkv_norm"], (self.rank,), role="gain", init="one_plus_normal")]
-        specs += [ParamSpec(n["uk"], (self.heads * self.dim, self.rank)), ParamSpec(n["uv"], (self.heads * self.vdim, self.rank)),
-                  ParamSpec(n["o"], (h, self.heads * self.vdim))]
+        specs += [ParamSpec(n["uk"], (self.heads * self.dim, self.rank)), ParamSpec(n["uv"], (self.heads * self.vdim, self.rank))]
+        if self.gated:
+            specs.append(ParamSpec(n["g"], (self.heads, h)))
+        specs.append(ParamSpec(n["o"], (h, self.heads * self.vdim)))
         return specs
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         n = self.names
-        if self.shares_cache:
-            self.proj = tensors[n["q"]].contiguous()
-        else:
-            self.proj = torch.cat([tensors[n["q"]], tensors[n["dkv"]]], dim=0).contiguous()
+        q_w = tensors[n["q"]]
+        order = None
+        if self.interleaved and self.rot_dim:  # pairs of neighbours become pairs half the part apart
+            order = torch.cat([torch.arange(0, self.rot_dim, 2), torch.arange(1, self.rot_dim, 2)]).to(q_w.device)
+            q_w = q_w.reshape(self.heads, self.q_head, -1)
+            q_w = torch.cat([q_w[:, :self.dim], q_w[:, self.dim:][:, order]], dim=1).reshape(self.q_width, -1)
+        stacked = [q_w]
+        if not self.shares_cache:
+            down = tensors[n["dkv"]]
+            if order is not None:
+                down = torch.cat([down[:self.rank], down[self.rank:][order]], dim=0)
+            stacked.append(down)
             self.norm_w = tensors[n["dkv_norm"]].contiguous()
+        if self.gated:
+            stacked.append(tensors[n["g"]])
+        self.proj = torch.cat(stacked, dim=0).contiguous()
         # [heads, rank, dim]: a head's rows are the columns of its Wuk, so that q~ = Wuk^T q_plain is a product by rows
         self.uk_t = tensors[n["uk"]].reshape(self.heads, self.dim, self.rank).transpose(1, 2).contiguous()
         self.uv = tensors[n["uv"]].reshape(self.heads, self.vdim, self.rank).contiguous()
@@ -174,7 +197,7 @@ class LatentAttention(Mixer):
         table = batch.block_tables[cache.group]
         projected = ctx.buffer("latent_attn.proj", (n, self.proj_width))
         linear(x, self.proj, projected, None, n, ctx)
-        down = None if self.shares_cache else projected[:, self.q_width:]
+        down = None if self.shares_cache else projected[:, self.q_width:self.gate_first]
         carried = ctx.buffer("latent_attn.q", (n, self.heads * self.row))  # per head [q~ | rotated part]
         kernels.latent_prepare(projected, down, self.norm_w, self.inv_freq, self.amplitude, batch.positions,
                                batch.seq_of_token, table, cache.k_pages, n, self.heads, self.dim, self.rot_dim, self.rank,
@@ -192,7 +215,8 @@ class LatentAttention(Mixer):
             kernels.latent_attention(carried, mixed, cache.k_pages, table, batch.seq_of_token, batch.positions, n, self.heads,
                                      self.rank, self.rot_dim, self.window, self.scale, ctx.status)
         values = ctx.buffer("latent_attn.values", (n, self.heads * self.vdim))
-        kernels.head_linear(mixed, self.rank, self.uv, values, self.vdim, n)
+        kernels.head_linear(mixed, self.rank, self.uv, values, self.vdim, n,
+                            gate=projected[:, self.gate_first:] if self.gated else None)
         out = ctx.buffer("latent_attn.out", (n, self.hidden_size))
         linear(values, self.out_w, out, None, n, ctx)
         return out

@@ -15,8 +15,14 @@ portions of prompts puts the pairs in expert order too, reads the experts' row c
 expert's rows as one matrix product through :func:`~turboserve_b200.ops.linear.linear`; a kernel adds the
 weighted rows up per token in a fixed order.
 
+Options: ``score`` ``"sigmoid"`` scores every expert on its own, ``s = sigmoid(z)``; ``renormalize`` ``False`` uses the
+chosen scores as weights as they are; ``weight_on`` ``"input"`` puts the weight on what the expert reads, ``sum
+expert(w h)``, instead of on what it gives (an expert is not linear, so the two differ; since gate and up are,
+``gate(w h) = w gate(h)`` and the factor enters on their sums in fp32 before the activation).
+
 Parameters: ``experts``, ``top``, ``groups``, ``keep``, ``intermediate_size``, ``shared`` (intermediate size of
-the shared expert, or ``None``), ``activation``; ``names``: ``router``, ``expert`` (a pattern with ``{index}``),
+the shared expert, or ``None``), ``activation``, ``shared_activation`` (default: the experts'), ``score``,
+``renormalize``, ``weight_on``; ``names``: ``router``, ``expert`` (a pattern with ``{index}``),
 ``shared`` (a prefix), and ``gate up down`` (the matrices' names behind those prefixes).
 """
 
@@ -55,13 +61,18 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"{self.experts} experts do not form {self.groups} equal groups of which {self.keep} are kept")
         if self.keep * (self.experts // self.groups) < self.top:
             raise ValueError("the kept groups hold fewer experts than are to be chosen")
+        self.score = str(spec.get("score", "softmax"))
+        self.renormalize = bool(spec.get("renormalize", True))
+        self.weight_on = str(spec.get("weight_on", "output"))
+        if self.score not in ("softmax", "sigmoid") or self.weight_on not in ("input", "output"):
+            raise ValueError(f"scores are 'softmax' or 'sigmoid' and weights stand on 'input' or 'output', got {self.score!r}, {self.weight_on!r}")
         self.names = {**DEFAULT_NAMES, **dict(spec.get("names") or {})}
         self.dtype = dtype
         shared = spec.get("shared")
         self.shared = None
         if shared:
             inner = {role: self.names["shared"] + self.names[role] for role in ("gate", "up", "down")}
-            self.shared = GatedMLP(PartSpec("gated_mlp", dict(intermediate_size=int(shared), activation=self.activation, names=inner)),
+            self.shared = GatedMLP(PartSpec("gated_mlp", dict(intermediate_size=int(shared), activation=str(spec.get("shared_activation") or self.activation), names=inner)),
                                    hidden_size, dtype, device)
         self.router: torch.Tensor | None = None
         self.gate_up: torch.Tensor | None = None  # [experts, 2 * ff, hidden]: an expert's gate rows, then its up rows
@@ -97,7 +108,9 @@ class RoutedExperts(FeedForward):
         n, top = batch.num_tokens, self.top
         chosen = ctx.buffer("moe.chosen", (n, top), torch.int32)
         weights = ctx.buffer("moe.weights", (n, top), torch.float32)
-        kernels.moe_route(x, self.router, chosen, weights, n, top, self.groups, self.keep)
+        kernels.moe_route(x, self.router, chosen, weights, n, top, self.groups, self.keep, self.score, self.renormalize)
+        # the weight stands on one side of an expert: on what it reads, or on what it gives
+        w_in, w_out = (weights, None) if self.weight_on == "input" else (None, weights)
         always = self.shared.forward(x, ctx) if self.shared is not None else None
         out = ctx.buffer("moe.out", (n, self.hidden_size))
         pairs = n * top
@@ -112,17 +125,17 @@ class RoutedExperts(FeedForward):
         moved = ctx.buffer("moe.rows_out", (pairs, self.hidden_size))
         if batch.max_query_len <= 1:
             if pairs <= PAIRS_ALONE or 8 * max(self.hidden_size, self.ff) * x.element_size() > kernels.MOE_EXPERT_ROWS_SMEM:
-                kernels.moe_pair_gate_up(x, self.gate_up, chosen, hidden, n, top, self.activation)
-                kernels.moe_pair_down(hidden, self.down, chosen, weights, always, out, n, top)
+                kernels.moe_pair_gate_up(x, self.gate_up, chosen, hidden, n, top, self.activation, in_weights=w_in)
+                kernels.moe_pair_down(hidden, self.down, chosen, w_out, always, out, n, top)
                 return out
             # a batch of single tokens: an expert's rows are streamed once for all the tokens that chose it
             kernels.moe_sort(chosen, pairs, self.experts, counters, place, pair_of_row)
-            kernels.moe_expert_rows(True, x, self.gate_up, counters, pair_of_row, hidden, top, self.activation)
+            kernels.moe_expert_rows(True, x, self.gate_up, counters, pair_of_row, hidden, top, self.activation, in_weights=w_in)
             kernels.moe_expert_rows(False, hidden, self.down, counters, pair_of_row, moved, top)
-            kernels.moe_combine(moved, place, weights, always, out, n, top)
+            kernels.moe_combine(moved, place, w_out, always, out, n, top)
             return out
         kernels.moe_sort(chosen, pairs, self.experts, counters, place, pair_of_row)
-        kernels.moe_gather(x, pair_of_row, rows, pairs, top)
+        kernels.moe_gather(x, pair_of_row, rows, pairs, top, in_weights=w_in)
         first = counters[self.experts: 2 * self.experts + 1].tolist()  # the one read-back: where each expert's rows start
         for e in range(self.experts):
             a, b = first[e], first[e + 1]
@@ -133,7 +146,7 @@ class RoutedExperts(FeedForward):
             a, b = first[e], first[e + 1]
             if b > a:
                 linear(hidden[a:b], self.down[e], moved[a:b], None, b - a, ctx)
-        kernels.moe_combine(moved, place, weights, always, out, n, top)
+        kernels.moe_combine(moved, place, w_out, always, out, n, top)
         return out
 
 

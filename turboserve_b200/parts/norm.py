@@ -13,7 +13,7 @@ import torch
 
 from ..config.model_spec import PartSpec
 from ..ops import kernels
-from .base import Norm, ParamSpec, pending_updates, register_norm
+from .base import Norm, NormedUpdate, ParamSpec, pending_updates, register_norm
 
 
 class RMSNorm(Norm):
@@ -47,7 +47,21 @@ class RMSNorm(Norm):
     def scratch_per_token(self) -> int:
         return 0  # it writes into the block's buffer
 
-    def forward(self, residual, delta, out, ctx, shift=None):
+    def forward(self, residual, delta, out, ctx, shift=None, rows_added=None):
+        """``rows_added``: a float32 matrix, a row a token, that enters the sum as well."""
+        if isinstance(delta, NormedUpdate) or rows_added is not None:
+            n = ctx.batch.num_tokens
+            if isinstance(delta, NormedUpdate):
+                if shift is None:  # the pending update's own norm, the rows and this norm in one pass
+                    kernels.norm_add_norm(residual, delta.update, delta.gain, delta.eps, rows_added, self.gain, self.eps, out, n)
+                    return out
+                kernels.norm_add_norm(residual, delta.update, delta.gain, delta.eps, rows_added, None, 0.0, None, n, out.dtype)
+                delta = None
+            elif shift is None and delta is None:
+                kernels.norm_add_norm(residual, None, None, 0.0, rows_added, self.gain, self.eps, out, n)
+                return out
+            else:
+                kernels.norm_add_norm(residual, None, None, 0.0, rows_added, None, 0.0, None, n, out.dtype)
         updates, mult = pending_updates(delta)
         if len(updates) <= 1 and shift is None and mult == 1.0:
             kernels.add_rmsnorm(residual, updates[0] if updates else None, self.gain, self.eps, out, None, ctx.batch.num_tokens)
@@ -64,6 +78,10 @@ class RMSNorm(Norm):
                             num_rows=ctx.batch.num_tokens, mult=mult)
         return out, out_other
 
+    def normed(self, update: torch.Tensor) -> NormedUpdate:
+        """``update`` as a pending update that enters the stream through this norm."""
+        return NormedUpdate(update, self.gain, self.eps)
+
     def forward_output(self, residual, update, mult: float, copy, ctx):
         """The norm behind a sublayer: ``residual += mult * norm(update)`` with this norm's gain, the statistics
         taken over ``update`` alone; ``copy`` (or ``None``) receives the new residual in the activation type."""
@@ -71,6 +89,9 @@ class RMSNorm(Norm):
         return copy
 
     def forward_rows(self, residual, delta, rows, num_rows, out, ctx):
+        if isinstance(delta, NormedUpdate):
+            kernels.norm_add_norm(residual, delta.update, delta.gain, delta.eps, None, self.gain, self.eps, out, num_rows, rows=rows)
+            return out
         updates, mult = pending_updates(delta)
         if len(updates) <= 1 and mult == 1.0:
             kernels.add_rmsnorm(residual, updates[0] if updates else None, self.gain, self.eps, out, rows, num_rows)

@@ -60,6 +60,38 @@ def scaled_rotary_frequencies(dims: int, base: float, scaling: dict | None = Non
     return freq.to(torch.float32), amplitude
 
 
+def wavelength_scaled_frequencies(dims: int, base: float, scaling: dict | None = None) -> torch.Tensor:
+    """Frequencies ``f_i = base^(-2i / dims)`` of ``dims / 2`` pairs, long waves stretched by their wavelength.
+
+    With ``scaling = {factor, low, high, original}`` and ``l_i = 2 pi / f_i``: a wave shorter than ``original / high``
+    is kept, one longer than ``original / low`` turns ``factor`` times slower (``f_i / factor``), and between the two
+    ``s = (original / l_i - low) / (high - low)`` blends them, ``(1 - s) f_i / factor + s f_i``. Computed in
+    float64 and rounded to float32 once (the angles are float32 products).
+    """
+    import math
+
+    if dims < 2 or dims % 2:
+        raise ValueError(f"rotary dims must be even and >= 2, got {dims}")
+    freq = float(base) ** (-2.0 * torch.arange(dims // 2, dtype=torch.float64) / dims)
+    if scaling:
+        factor, low, high, original = (float(scaling[key]) for key in ("factor", "low", "high", "original"))
+        if not (factor > 0.0 and high > low and original > 0.0):
+            raise ValueError("frequency scaling needs factor > 0, high > low and original > 0")
+        wave = 2.0 * math.pi / freq
+        blend = ((original / wave - low) / (high - low)).clamp(0.0, 1.0)
+        mixed = (1.0 - blend) * freq / factor + blend * freq
+        freq = torch.where(wave < original / high, freq, torch.where(wave > original / low, freq / factor, mixed))
+    return freq.to(torch.float32)
+
+
+def rotary_frequencies(dims: int, base: float, scaling: dict | None = None) -> tuple[torch.Tensor, float]:
+    """Frequencies and the factor on cos and sin for either way of scaling: ``{factor, original, fast, slow}``
+    (:func:`scaled_rotary_frequencies`) or ``{factor, low, high, original}`` (:func:`wavelength_scaled_frequencies`)."""
+    if scaling and "low" in scaling and "high" in scaling:
+        return wavelength_scaled_frequencies(dims, base, scaling), 1.0
+    return scaled_rotary_frequencies(dims, base, scaling)
+
+
 class NoPosition(PositionEncoding):
     """No position encoding: queries and keys are used as projected (bias and append only)."""
 

@@ -48,6 +48,10 @@ class LinearHead(LogitHead):
         self.hidden_size, self.vocab_size, self.tied = int(hidden_size), int(vocab_size), bool(tied)
         self.scale = float(spec.get("scale", 1.0))
         """The logits are multiplied by it (in float32, after the product)."""
+        self.softcap = float(spec.get("softcap") or 0.0)
+        """If positive the logits are bent into ``(-softcap, softcap)``: ``softcap * tanh(logits / softcap)``, in float32, last."""
+        if self.softcap < 0.0:
+            raise ValueError("a head's softcap must be positive (or absent)")
         self.tensor = str(spec.get("tensor", "weight"))
         """The matrix's local name in the checkpoint."""
         self.weight: torch.Tensor | None = None
@@ -71,6 +75,8 @@ class LinearHead(LogitHead):
         linear(rows_in, self.weight, logits, None, num_rows, ctx)
         if self.scale != 1.0:
             kernels.scale_rows(logits, self.scale, num_rows)
+        if self.softcap:
+            kernels.softcap_rows(logits, self.softcap, num_rows)
 
 
 class ShiftTable(StreamShifts):
