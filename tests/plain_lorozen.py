@@ -198,10 +198,18 @@ def run_order(config: dict) -> list[tuple[int, bool]]:
     return order + [(i, False) for i in range(stop, count)]
 
 
-def forward(config: dict, weights: dict, tokens: list[int]) -> tuple[torch.Tensor, torch.Tensor]:
-    """Logits [T, vocab] and the stream after every layer run [runs, T, width], both float64."""
+def forward(config: dict, weights: dict, tokens: list[int], jitter: float = 0.0) -> tuple[torch.Tensor, torch.Tensor]:
+    """Logits [T, vocab] and the stream after every layer run [runs, T, width], both float64.
+
+    With ``jitter`` every sublayer's input and output is multiplied, element by element, by ``1 + jitter * noise``
+    (standard normal noise from a fixed seed): what arithmetic of that relative precision may do to the logits."""
     w = {name: t.to(F64) for name, t in weights.items()}
     eps = float(config["norm"]["eps"])
+    noise = torch.Generator().manual_seed(1234)
+
+    def shaken(t: torch.Tensor) -> torch.Tensor:
+        return t if not jitter else t * (1.0 + jitter * torch.randn(t.shape, generator=noise, dtype=F64))
+
     embedded = w["embed"][torch.tensor(tokens, dtype=torch.long)]
     x = embedded.clone()
     streams = []
@@ -210,13 +218,13 @@ def forward(config: dict, weights: dict, tokens: list[int]) -> tuple[torch.Tenso
         if again:
             x = x + embedded
         own = part(w, f"l{index}.")
-        mixed = MIXERS[layer["type"]](rms_norm(x, own["norm1"], eps), part(own, "mix."), layer["mixer"], eps)
-        x = x + rms_norm(mixed, own["norm1b"], eps)
+        mixed = MIXERS[layer["type"]](shaken(rms_norm(x, own["norm1"], eps)), part(own, "mix."), layer["mixer"], eps)
+        x = x + rms_norm(shaken(mixed), own["norm1b"], eps)
         if layer.get("mlp"):
-            moved = feed_forward(rms_norm(x, own["norm2"], eps), part(own, "mlp."), layer["mlp"])
-            x = x + rms_norm(moved, own["norm2b"], eps)
+            moved = feed_forward(shaken(rms_norm(x, own["norm2"], eps)), part(own, "mlp."), layer["mlp"])
+            x = x + rms_norm(shaken(moved), own["norm2b"], eps)
         streams.append(x.clone())
-    logits = rms_norm(x, w["final.norm"], eps) @ w["head"].T
+    logits = shaken(rms_norm(x, w["final.norm"], eps)) @ w["head"].T
     cap = config.get("logit_softcap")
     if cap:
         logits = float(cap) * torch.tanh(logits / float(cap))
