@@ -674,6 +674,31 @@ def begovik_raw(width: int, layers: int) -> dict:
             "norm": {"eps": 1e-6}, "initializer_range": 0.02, "layers": [pattern[i % 4] for i in range(layers)]}
 
 
+def lorozen_raw(width: int, layers: int) -> dict:
+    """Lorozen at the sizes of a real model's layers, ``layers`` layer runs in all: latent attention, wkv time mixing and
+    two layers of attention in turn (l, w, a, a, l, w, ...), of which the second and third are a stretch that runs twice
+    (so the model has ``layers - 2`` layers of weights). Latent attention: heads of 128 plain and 64 rotated query
+    elements and 128 values over a latent of 512, a window of 1,024, a gate per head. Attention: heads of 128 keys and
+    values, four query heads to a key head, 64 rotated elements with stretched long waves, biases, a learned sink, a
+    window of 1,024. wkv: heads of 64, a decay pair of rank 64. The first layer's feed-forward is dense (4 x width); the
+    others are mixtures of 8 experts of ``width`` features of which 2 are chosen by sigmoid scores, the weight on the
+    expert's input, beside a shared expert of width / 2. The logits are capped at 30."""
+    heads = max(4, width // 128)
+    latent = dict(heads=heads, dim=128, rot_dim=64, vdim=128, kv_rank=512, scale=192 ** -0.5, mask={"size": DESIGN_WINDOW},
+                  rot={"base": 10000.0, "dims": 64})
+    attention = dict(heads=heads, kv_heads=heads // 4, dim=128, vdim=128, scale=128 ** -0.5, mask={"size": DESIGN_WINDOW},
+                     rot={"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})
+    wkv = dict(heads=width // 64, dim=64, decay_rank=64)
+    moe = {"kind": "moe", "expert": {"ff": width}, "router": {"experts": 8, "top": 2}, "shared": {"ff": width // 2}}
+    pattern = [("latent_attention", latent), ("wkv", wkv), ("attention", attention), ("attention", attention)]
+    out = []
+    for i in range(layers - 2):
+        kind, mixer = pattern[i % 4]
+        out.append({"type": kind, "mixer": mixer, "mlp": {"kind": "dense", "ff": 4 * width} if i == 0 else moe})
+    return {"architecture": "Lorozen", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+            "loop": {"start": 1, "stop": 3, "times": 2}, "initializer_range": 0.02, "layers": out}
+
+
 class OpTimer:
     """CUDA events around every kernel entry point and matrix product a step calls, summed by name."""
 
@@ -706,7 +731,7 @@ class OpTimer:
                      "diff_attention", "diff_attention_mma", "ssd_scan", "gated_group_norm", "scale_rows", "norm_add",
                      "latent_prepare", "head_linear", "latent_attention", "latent_gather", "latent_softmax", "retention_scan",
                      "head_norm_gate", "head_norm_rope_write", "paged_attention_capped", "paged_attention_capped_mma", "norm_pair_mix",
-                     "shift_mix", "selective_scan", "chosen_decay_scan", "part_norm_gate", "moe_route", "moe_pair_gate_up", "moe_pair_down", "moe_expert_rows", "moe_sort", "moe_gather", "moe_combine"):
+                     "shift_mix", "selective_scan", "chosen_decay_scan", "part_norm_gate", "norm_add_norm", "softcap_rows", "moe_route", "moe_pair_gate_up", "moe_pair_down", "moe_expert_rows", "moe_sort", "moe_gather", "moe_combine"):
             if hasattr(kernels, name):
                 self._wrap(kernels, name, name)
         for module in (attention, diff_attention, mamba2, mlp, vocabulary, latent_attention, retention, sink_attention, wkv, mamba1):
@@ -763,7 +788,8 @@ def design_bench(size: str, steps: int, warmup: int, tokens: int = 2048, context
     peaks = load_peaks()
     of = "of measured" if peaks["source"] == "measured" else "of fallback"
     hbm, tensor = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
-    titles = {"filezen": "Filezen beside Baporax and Qwen2", "begovik": "Begovik beside Baporax and Qwen2", "baporax": "Baporax beside Qwen2"}
+    titles = {"filezen": "Filezen beside Baporax and Qwen2", "begovik": "Begovik beside Baporax and Qwen2", "baporax": "Baporax beside Qwen2",
+              "lorozen": "Lorozen beside Filezen, Begovik and Qwen2"}
     out = {"design": titles[design] + " at equal size",
            "width": width, "layers": layers, "prompt_tokens": tokens,
            "decode_context": context, "window": DESIGN_WINDOW, "dtype": "bf16", "peaks": of, "models": {}}
@@ -773,6 +799,9 @@ def design_bench(size: str, steps: int, warmup: int, tokens: int = 2048, context
         models.insert(0, ("filezen", filezen_raw(width, layers)))
     if design == "begovik":
         models.insert(0, ("begovik", begovik_raw(width, layers)))
+    if design == "lorozen":  # beside the models whose mixers and feed-forwards are nearest to its own
+        models = [("lorozen", lorozen_raw(width, layers)), ("filezen", filezen_raw(width, layers)),
+                  ("begovik", begovik_raw(width, layers)), ("qwen2", qwen2_equal_raw(width, layers))]
     if alone:
         models = [m for m in models if m[0] == design]
     for name, raw in models:
@@ -801,7 +830,44 @@ def design_bench(size: str, steps: int, warmup: int, tokens: int = 2048, context
         # the mixers' kernels against their rooflines (time of all layers of the kind in one step)
         kernels_out = {}
         seen = min(context, DESIGN_WINDOW)
-        if name == "begovik":
+        if name == "lorozen":
+            runs = [raw["layers"][run.layer] for run in config.to_model_spec().order]
+            entry["layer_runs"] = len(runs)
+            attention_runs = sum(1 for layer in runs if layer["type"] == "attention")
+            latent_runs = sum(1 for layer in runs if layer["type"] == "latent_attention")
+            wkv_runs = len(runs) - attention_runs - latent_runs
+            moe_runs = sum(1 for layer in runs if layer["mlp"]["kind"] == "moe")
+            w_heads, row = width // 64, 512 + 64
+            prefill = entry["prefill_ops_us"]
+            flops = attention_runs * visible_pairs(tokens, DESIGN_WINDOW) * heads * 4 * 128
+            us = prefill.get("paged_attention_capped_mma", 0.0) + prefill.get("paged_attention_capped", 0.0)
+            kernels_out["attention_prefill"] = {"us": us, "tflops": round(flops / us / 1e6, 1), "frac_tensor": round(flops / (us * 1e-6) / tensor, 4)}
+            flops = latent_runs * visible_pairs(tokens, DESIGN_WINDOW) * heads * (2 * row + 2 * 512)
+            us = sum(prefill.get(k, 0.0) for k in ("latent_attention", "latent_products", "latent_softmax", "latent_gather"))
+            kernels_out["latent_prefill"] = {"us": us, "tflops": round(flops / us / 1e6, 1), "frac_tensor": round(flops / (us * 1e-6) / tensor, 4)}
+            scan_flops = wkv_runs * tokens * w_heads * 64 * 64 * 6
+            us = prefill.get("chosen_decay_scan", 0.0)
+            kernels_out["wkv_prefill"] = {"us": us, "fp32_tflops": round(scan_flops / us / 1e6, 2)}
+            norm_bytes = 2 * len(runs) * tokens * width * (4 + 4 + 2 + 2)  # residual read and written, an update read, a row written
+            us = prefill.get("norm_add_norm", 0.0) + prefill.get("add_rmsnorm", 0.0)
+            kernels_out["norms_prefill"] = {"us": us, "gbs": round(norm_bytes / us / 1e3, 1), "frac_hbm": round(norm_bytes / (us * 1e-6) / hbm, 4)}
+            entry["active_params_per_token"] = model.num_parameters() - sum(
+                1 for layer in raw["layers"] if layer["mlp"]["kind"] == "moe") * 6 * 3 * width * width
+            for batch in (8, 64):
+                ops = entry[f"decode_b{batch}_ops_us"]
+                bytes_read = attention_runs * batch * seen * (heads // 4) * 256 * 2
+                us = ops.get("paged_attention_capped", 0.0) + ops.get("paged_attention_capped_mma", 0.0)
+                kernels_out[f"attention_decode_b{batch}"] = {"us": us, "gbs": round(bytes_read / us / 1e3, 1), "frac_hbm": round(bytes_read / (us * 1e-6) / hbm, 4)}
+                bytes_read = latent_runs * batch * seen * row * 2
+                us = ops.get("latent_attention", 0.0)
+                kernels_out[f"latent_decode_b{batch}"] = {"us": us, "gbs": round(bytes_read / us / 1e3, 1), "frac_hbm": round(bytes_read / (us * 1e-6) / hbm, 4)}
+                state_bytes = wkv_runs * batch * w_heads * 64 * 64 * 4 * 2
+                us = ops.get("chosen_decay_scan", 0.0)
+                kernels_out[f"wkv_decode_b{batch}"] = {"us": us, "gbs": round(state_bytes / us / 1e3, 1), "frac_hbm": round(state_bytes / (us * 1e-6) / hbm, 4)}
+                expert_bytes = moe_runs * min(batch * 2, 8) * 3 * width * width * 2
+                us = sum(ops.get(k, 0.0) for k in ("moe_pair_gate_up", "moe_pair_down", "moe_expert_rows"))
+                kernels_out[f"experts_decode_b{batch}"] = {"us": us, "gbs": round(expert_bytes / us / 1e3, 1), "frac_hbm": round(expert_bytes / (us * 1e-6) / hbm, 4)}
+        elif name == "begovik":
             # attention without a window: a prompt's rows see everything before them, a decoded token its whole context
             side_layers = sum(1 for layer in raw["layers"] if layer["type"] == "parallel")
             scan_layers = sum(1 for layer in raw["layers"] if layer["type"] == "mamba1")
@@ -914,7 +980,7 @@ def main() -> int:
     parser.add_argument("--sampling-sweep", action="store_true", help="time decode steps through LLMEngine under a few sets of sampling options and exit")
     parser.add_argument("--fp32-products", action="store_true", help="time the float32 path's matrix product at the 7B shapes and exit")
     parser.add_argument("--float32", action="store_true", help="with --one-step: the true 32-bit path")
-    parser.add_argument("--design", choices=["baporax", "filezen", "begovik"], default=None,
+    parser.add_argument("--design", choices=["baporax", "filezen", "begovik", "lorozen"], default=None,
                         help="measure that design at real layer sizes beside Qwen2 at equal size and exit (see design_bench())")
     parser.add_argument("--design-size", choices=sorted(DESIGN_SIZES), default="2k", help="width and depth for --design")
     parser.add_argument("--design-alone", action="store_true", help="with --design: leave the models beside it out (profiling runs)")

@@ -13,7 +13,9 @@ scores stand out in the softmax (a key at the far edge of a window then moves th
 sinks get values from -3 to 3 (so that in some heads the sink takes most of the weight and in others next to none), and
 the wkv decays' offsets are so low that a state lost or mixed up hundreds of tokens earlier still shows in the output.
 
-``steady_routing`` makes every router's choice a plain function of the token with wide margins (see there).
+``steady_routing`` makes every router's choice a plain function of the token with wide margins, and
+``steady_first_outputs`` keeps a wkv layer's output at a request's first token from hanging on the sign of a sum that
+nearly cancels (see there): both are steps of the design that one rounding can turn round with nothing being wrong.
 """
 
 from __future__ import annotations
@@ -127,6 +129,7 @@ def write_raw(raw: dict, seed: int, folder: Path, sharp: bool = False, steady: b
     for entry in written["layers"]:  # a folder does not say how wide the decay's pair is: the tensors' shapes do
         entry["mixer"].pop("decay_rank", None)
     (Path(folder) / "config.json").write_text(json.dumps(written))
+    steady_first_outputs(folder)
     if sharp:
         sharpen(folder)
     if steady:
@@ -141,6 +144,23 @@ def _rewrite(folder: Path, change) -> None:
     tensors = load_file(str(path))
     change(tensors)
     save_file({k: v.contiguous() for k, v in tensors.items()}, str(path), metadata={"format": "pt"})
+
+
+def steady_first_outputs(folder: Path) -> None:
+    """Keep a wkv layer's output at a request's first token away from a coin toss.
+
+    There the state is empty and a head gives ``(sum_k r_k u_k k_k) v``: one vector times a sum that, with random signs,
+    nearly cancels for one token in a hundred. The norm behind the mixer brings the output to unit size however small it
+    is, so whether such a sum comes out just above or just below zero (which one rounding to bfloat16 decides) turns
+    the whole update round, with nothing being wrong. The folders of the tests therefore get receptance matrices that
+    are the key matrices plus a part of their own, and positive bonuses: the sum is then mostly one of squares."""
+    def change(tensors):
+        for name in list(tensors):
+            if name.endswith(".mix.r") and name[:-1] + "k" in tensors and name[:-1] + "u" in tensors:
+                tensors[name] = (tensors[name[:-1] + "k"].float() + 0.5 * tensors[name].float()).to(torch.bfloat16)
+                tensors[name[:-1] + "u"] = (0.5 + 4.0 * tensors[name[:-1] + "u"].float().abs()).to(torch.bfloat16)
+
+    _rewrite(folder, change)
 
 
 def sharpen(folder: Path) -> None:

@@ -18,6 +18,17 @@ import torch
 
 F64 = torch.float64
 
+_SHAKE: list = []
+"""While a shaken run is under way: ``[jitter, generator]``. :func:`made` then multiplies what a matrix product gives,
+element by element, by ``1 + jitter * noise``: what arithmetic that rounds such results to that precision may do."""
+
+
+def made(t: torch.Tensor) -> torch.Tensor:
+    """The result of a matrix product (or a sublayer's input or output): itself, or shaken in a shaken run."""
+    if not _SHAKE:
+        return t
+    return t * (1.0 + _SHAKE[0] * torch.randn(t.shape, generator=_SHAKE[1], dtype=F64))
+
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor | None, eps: float) -> torch.Tensor:
     y = x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps)
@@ -92,9 +103,9 @@ def attention(h: torch.Tensor, w: dict, sizes: dict, eps: float) -> torch.Tensor
     heads, kv_heads = int(sizes["heads"]), int(sizes.get("kv_heads") or sizes["heads"])
     dim, vdim = int(sizes["dim"]), int(sizes.get("vdim") or sizes["dim"])
     tokens = h.shape[0]
-    q = (h @ w["q"].T + w["q.b"]).reshape(tokens, heads, dim)
-    k = (h @ w["k"].T + w["k.b"]).reshape(tokens, kv_heads, dim)
-    v = (h @ w["v"].T + w["v.b"]).reshape(tokens, kv_heads, vdim)
+    q = made(h @ w["q"].T + w["q.b"]).reshape(tokens, heads, dim)
+    k = made(h @ w["k"].T + w["k.b"]).reshape(tokens, kv_heads, dim)
+    v = made(h @ w["v"].T + w["v.b"]).reshape(tokens, kv_heads, vdim)
     q, k = rotate(q, sizes.get("rot"), False), rotate(k, sizes.get("rot"), False)
     per = heads // kv_heads
     k, v = k.repeat_interleave(per, dim=1), v.repeat_interleave(per, dim=1)
@@ -102,7 +113,7 @@ def attention(h: torch.Tensor, w: dict, sizes: dict, eps: float) -> torch.Tensor
     scores = scores.masked_fill(~seen(tokens, window_of(sizes)), -math.inf)
     sink = w["sink"].reshape(heads, 1, 1).expand(heads, tokens, 1)
     weights = torch.softmax(torch.cat([scores, sink], dim=-1), dim=-1)[..., :tokens]
-    return torch.einsum("hts,shv->thv", weights, v).reshape(tokens, heads * vdim) @ w["o"].T
+    return made(torch.einsum("hts,shv->thv", weights, v).reshape(tokens, heads * vdim)) @ w["o"].T
 
 
 def latent_attention(h: torch.Tensor, w: dict, sizes: dict, eps: float) -> torch.Tensor:
@@ -111,8 +122,8 @@ def latent_attention(h: torch.Tensor, w: dict, sizes: dict, eps: float) -> torch
     heads, dim, rot_dim = int(sizes["heads"]), int(sizes["dim"]), int(sizes["rot_dim"])
     vdim, rank = int(sizes["vdim"]), int(sizes["kv_rank"])
     tokens = h.shape[0]
-    q = (h @ w["q"].T).reshape(tokens, heads, dim + rot_dim)
-    down = h @ w["dkv"].T
+    q = made(h @ w["q"].T).reshape(tokens, heads, dim + rot_dim)
+    down = made(h @ w["dkv"].T)
     latent = rms_norm(down[:, :rank], w["dkv.norm"], eps)
     shared = rotate(down[:, None, rank:], sizes.get("rot"), True)[:, 0]
     q_plain, q_turned = q[..., :dim], rotate(q[..., dim:], sizes.get("rot"), True)
@@ -121,8 +132,8 @@ def latent_attention(h: torch.Tensor, w: dict, sizes: dict, eps: float) -> torch
     scores = (torch.einsum("thd,shd->hts", q_plain, keys) + torch.einsum("thd,sd->hts", q_turned, shared)) * float(sizes["scale"])
     scores = scores.masked_fill(~seen(tokens, window_of(sizes)), -math.inf)
     mixed = torch.einsum("hts,shv->thv", torch.softmax(scores, dim=-1), values)
-    gate = torch.sigmoid(h @ w["g"].T)  # [T, heads]
-    return (mixed * gate[:, :, None]).reshape(tokens, heads * vdim) @ w["o"].T
+    gate = torch.sigmoid(made(h @ w["g"].T))  # [T, heads]
+    return made((mixed * gate[:, :, None]).reshape(tokens, heads * vdim)) @ w["o"].T
 
 
 def wkv(h: torch.Tensor, w: dict, sizes: dict, eps: float) -> torch.Tensor:
@@ -132,11 +143,11 @@ def wkv(h: torch.Tensor, w: dict, sizes: dict, eps: float) -> torch.Tensor:
     tokens = h.shape[0]
     before = torch.cat([torch.zeros_like(h[:1]), h[:-1]], dim=0)
     blend = {s: h + (before - h) * w["mu." + s] for s in "rkvgw"}
-    r = (blend["r"] @ w["r"].T).reshape(tokens, heads, dim)
-    k = (blend["k"] @ w["k"].T).reshape(tokens, heads, dim)
-    v = (blend["v"] @ w["v"].T).reshape(tokens, heads, dim)
-    gate = silu(blend["g"] @ w["g"].T)
-    decay = torch.exp(-torch.exp(torch.tanh(blend["w"] @ w["w1"].T) @ w["w2"].T + w["w0"])).reshape(tokens, heads, dim)
+    r = made(blend["r"] @ w["r"].T).reshape(tokens, heads, dim)
+    k = made(blend["k"] @ w["k"].T).reshape(tokens, heads, dim)
+    v = made(blend["v"] @ w["v"].T).reshape(tokens, heads, dim)
+    gate = silu(made(blend["g"] @ w["g"].T))
+    decay = torch.exp(-torch.exp(made(torch.tanh(made(blend["w"] @ w["w1"].T))) @ w["w2"].T + w["w0"])).reshape(tokens, heads, dim)
     bonus = w["u"].reshape(heads, dim)
     state = torch.zeros(heads, dim, dim, dtype=h.dtype)  # [head, key channel, value channel]
     out = torch.zeros(tokens, heads, dim, dtype=h.dtype)
@@ -145,11 +156,11 @@ def wkv(h: torch.Tensor, w: dict, sizes: dict, eps: float) -> torch.Tensor:
         out[t] = torch.einsum("hkv,hk->hv", state + bonus[:, :, None] * outer, r[t])
         state = decay[t, :, :, None] * state + outer
     out = rms_norm(out, None, eps).reshape(tokens, heads * dim) * w["norm"] * gate
-    return out @ w["o"].T
+    return made(out) @ w["o"].T
 
 
 def gated(h: torch.Tensor, w: dict, prefix: str, act) -> torch.Tensor:
-    return (act(h @ w[prefix + "gate"].T) * (h @ w[prefix + "up"].T)) @ w[prefix + "down"].T
+    return made(act(made(h @ w[prefix + "gate"].T)) * made(h @ w[prefix + "up"].T)) @ w[prefix + "down"].T
 
 
 def route(h: torch.Tensor, router: torch.Tensor, top: int) -> tuple[torch.Tensor, torch.Tensor]:
@@ -201,15 +212,19 @@ def run_order(config: dict) -> list[tuple[int, bool]]:
 def forward(config: dict, weights: dict, tokens: list[int], jitter: float = 0.0) -> tuple[torch.Tensor, torch.Tensor]:
     """Logits [T, vocab] and the stream after every layer run [runs, T, width], both float64.
 
-    With ``jitter`` every sublayer's input and output is multiplied, element by element, by ``1 + jitter * noise``
-    (standard normal noise from a fixed seed): what arithmetic of that relative precision may do to the logits."""
+    With ``jitter`` the run is shaken: every sublayer's input and output and the result of every matrix product within
+    one is multiplied, element by element, by ``1 + jitter * noise`` (standard normal noise from a fixed seed)."""
+    if jitter:
+        _SHAKE[:] = [float(jitter), torch.Generator().manual_seed(1234)]
+    try:
+        return _forward(config, weights, tokens)
+    finally:
+        _SHAKE.clear()
+
+
+def _forward(config: dict, weights: dict, tokens: list[int]) -> tuple[torch.Tensor, torch.Tensor]:
     w = {name: t.to(F64) for name, t in weights.items()}
     eps = float(config["norm"]["eps"])
-    noise = torch.Generator().manual_seed(1234)
-
-    def shaken(t: torch.Tensor) -> torch.Tensor:
-        return t if not jitter else t * (1.0 + jitter * torch.randn(t.shape, generator=noise, dtype=F64))
-
     embedded = w["embed"][torch.tensor(tokens, dtype=torch.long)]
     x = embedded.clone()
     streams = []
@@ -218,13 +233,13 @@ def forward(config: dict, weights: dict, tokens: list[int], jitter: float = 0.0)
         if again:
             x = x + embedded
         own = part(w, f"l{index}.")
-        mixed = MIXERS[layer["type"]](shaken(rms_norm(x, own["norm1"], eps)), part(own, "mix."), layer["mixer"], eps)
-        x = x + rms_norm(shaken(mixed), own["norm1b"], eps)
+        mixed = MIXERS[layer["type"]](made(rms_norm(x, own["norm1"], eps)), part(own, "mix."), layer["mixer"], eps)
+        x = x + rms_norm(made(mixed), own["norm1b"], eps)
         if layer.get("mlp"):
-            moved = feed_forward(shaken(rms_norm(x, own["norm2"], eps)), part(own, "mlp."), layer["mlp"])
-            x = x + rms_norm(shaken(moved), own["norm2b"], eps)
+            moved = feed_forward(made(rms_norm(x, own["norm2"], eps)), part(own, "mlp."), layer["mlp"])
+            x = x + rms_norm(made(moved), own["norm2b"], eps)
         streams.append(x.clone())
-    logits = shaken(rms_norm(x, w["final.norm"], eps)) @ w["head"].T
+    logits = made(rms_norm(x, w["final.norm"], eps)) @ w["head"].T
     cap = config.get("logit_softcap")
     if cap:
         logits = float(cap) * torch.tanh(logits / float(cap))
