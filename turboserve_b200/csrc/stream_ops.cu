@@ -194,12 +194,129 @@ __global__ void norm_add_norm_kernel(float* __restrict__ residual, const T* __re
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<T>(row_cache[i] * inv_pre * gain_pre[i]);
 }
 
+// The same with 16-byte loads and stores, for rows whose width is a multiple of four and whose tensors are aligned:
+// a thread takes four neighbours a pass; the update and the residual are both fetched before the first sum is awaited
+// (two rows of shared memory), so the row's loads are all in flight together.  Every sum is taken as in the kernel
+// above: first the update's norm, then the residual, then the added rows.
+template <typename T> struct Four;
+template <> struct Four<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+    const float4 x = *reinterpret_cast<const float4*>(p);
+    v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <> struct Four<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 x = *reinterpret_cast<const uint2*>(p);
+    v[0] = __uint_as_float(x.x << 16); v[1] = __uint_as_float(x.x & 0xffff0000u);
+    v[2] = __uint_as_float(x.y << 16); v[3] = __uint_as_float(x.y & 0xffff0000u);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[4]) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 x;
+    x.x = *reinterpret_cast<unsigned*>(&a);
+    x.y = *reinterpret_cast<unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = x;
+  }
+};
+
+template <typename T>
+__global__ void norm_add_norm_vec_kernel(float* __restrict__ residual, const T* __restrict__ update,
+                                         const float* __restrict__ gain_post, float eps_post,
+                                         const float* __restrict__ extra, const float* __restrict__ gain_pre, float eps_pre,
+                                         T* __restrict__ out, const int* __restrict__ rows, int hidden) {
+  extern __shared__ __align__(16) float row_cache[];  // [2][hidden]: the update, the residual
+  __shared__ float scratch[33];
+  float* u_cache = row_cache;
+  float* x_cache = row_cache + hidden;
+  const int r = blockIdx.x;
+  pdl_wait();
+  pdl_trigger<32>();
+  const int src = rows ? rows[r] : r;
+  float* res = residual + (size_t)src * hidden;
+  const T* up = update ? update + (size_t)src * hidden : nullptr;
+  const float* ex = extra ? extra + (size_t)src * hidden : nullptr;
+  float sum_u = 0.0f;
+  for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+    float x[4];
+    Four<float>::load(res + i, x);
+    if (up) {
+      float u[4];
+      Four<T>::load(up + i, u);
+      Four<float>::store(u_cache + i, u);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sum_u = fmaf(u[e], u[e], sum_u);
+    }
+    Four<float>::store(x_cache + i, x);
+  }
+  const float inv_post = up ? 1.0f / sqrtf(block_sum(sum_u, scratch) / (float)hidden + eps_post) : 0.0f;
+  float sum_x = 0.0f;
+  for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+    float x[4];
+    Four<float>::load(x_cache + i, x);
+    if (up) {
+      float u[4], g[4];
+      Four<float>::load(u_cache + i, u);
+      Four<float>::load(gain_post + i, g);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) x[e] += u[e] * inv_post * g[e];
+    }
+    if (ex) {
+      float a[4];
+      Four<float>::load(ex + i, a);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) x[e] += a[e];
+    }
+    if (!rows && (up || ex)) Four<float>::store(res + i, x);
+    if (out) Four<float>::store(x_cache + i, x);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) sum_x = fmaf(x[e], x[e], sum_x);
+  }
+  if (!out) return;
+  const float inv_pre = 1.0f / sqrtf(block_sum(sum_x, scratch) / (float)hidden + eps_pre);
+  T* o = out + (size_t)r * hidden;
+  for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
+    float x[4], g[4];
+    Four<float>::load(x_cache + i, x);
+    Four<float>::load(gain_pre + i, g);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) x[e] = x[e] * inv_pre * g[e];
+    Four<T>::store(o + i, x);
+  }
+}
+
+template <typename T>
+static bool norm_add_norm_vec(float* residual, const void* update, const float* gain_post, float eps_post, const float* extra,
+                              const float* gain_pre, float eps_pre, void* out, const int* rows, int num_rows, int hidden,
+                              cudaStream_t stream) {
+  const size_t smem = (size_t)2 * hidden * sizeof(float);
+  const uintptr_t wide = (uintptr_t)residual | (uintptr_t)gain_post | (uintptr_t)extra | (uintptr_t)gain_pre;
+  const uintptr_t narrow = (uintptr_t)update | (uintptr_t)out;
+  if (hidden % 4 || smem > 200 * 1024 || (wide & 15) || (narrow & (sizeof(T) * 4 - 1))) return false;
+  int threads = (hidden / 4 + 31) / 32 * 32;
+  threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(norm_add_norm_vec_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  ts_launch(norm_add_norm_vec_kernel<T>, dim3(num_rows), dim3(threads), smem, stream, residual, (const T*)update, gain_post,
+            eps_post, extra, gain_pre, eps_pre, (T*)out, rows, hidden);
+  return true;
+}
+
 TS_EXPORT int ts_norm_add_norm(int dtype, float* residual, const void* update, const float* gain_post, float eps_post,
                                const float* extra, const float* gain_pre, float eps_pre, void* out, const int* rows,
                                int num_rows, int hidden, cudaStream_t stream) {
   if (num_rows <= 0) return 0;
   if (hidden < 1 || (size_t)hidden * sizeof(float) > 200 * 1024) return TS_ERR_SIZE;
   if ((update && !gain_post) || (out && !gain_pre)) return TS_ERR_ARGUMENT;
+  if (dtype == TS_F32 && norm_add_norm_vec<float>(residual, update, gain_post, eps_post, extra, gain_pre, eps_pre, out, rows,
+                                                   num_rows, hidden, stream))
+    return ts_launch_status();
+  if (dtype == TS_BF16 && norm_add_norm_vec<__nv_bfloat16>(residual, update, gain_post, eps_post, extra, gain_pre, eps_pre, out,
+                                                            rows, num_rows, hidden, stream))
+    return ts_launch_status();
   int threads = (hidden + 31) / 32 * 32;
   threads = threads < 64 ? 64 : (threads > 512 ? 512 : threads);
   const size_t smem = (size_t)hidden * sizeof(float);
