@@ -682,7 +682,7 @@ def lorozen_raw(width: int, layers: int) -> dict:
     values, four query heads to a key head, 64 rotated elements with stretched long waves, biases, a learned sink, a
     window of 1,024. wkv: heads of 64, a decay pair of rank 64. The first layer's feed-forward is dense (4 x width); the
     others are mixtures of 8 experts of ``width`` features of which 2 are chosen by sigmoid scores, the weight on the
-    expert's input, beside a shared expert of width / 2. The logits are capped at 30."""
+    expert's input, beside a shared expert of width / 2. The logits are capped at 50."""
     heads = max(4, width // 128)
     latent = dict(heads=heads, dim=128, rot_dim=64, vdim=128, kv_rank=512, scale=192 ** -0.5, mask={"size": DESIGN_WINDOW},
                   rot={"base": 10000.0, "dims": 64})
@@ -695,7 +695,7 @@ def lorozen_raw(width: int, layers: int) -> dict:
     for i in range(layers - 2):
         kind, mixer = pattern[i % 4]
         out.append({"type": kind, "mixer": mixer, "mlp": {"kind": "dense", "ff": 4 * width} if i == 0 else moe})
-    return {"architecture": "Lorozen", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
+    return {"architecture": "Lorozen", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 50.0,
             "loop": {"start": 1, "stop": 3, "times": 2}, "initializer_range": 0.02, "layers": out}
 
 

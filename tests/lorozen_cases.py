@@ -96,12 +96,12 @@ CASE_C = model(77, 100, 1e-6, [
 ], cap=7.5, loop=(1, 3, 3))
 # sizes of the tensor-core kernels: heads of 64 and 32, windows longer than a tile; a loop from the first layer on
 CASE_D = model(260, 128, 1e-5, [
-    layer(attention(8, 2, 64, 64, 0.125, 100, 10000.0, 32, (4.0, 1.0, 4.0, 128)), moe(8, 2, 64, 96)),
-    layer(latent(4, 32, 16, 32, 64, 0.14, 70, 250000.0), dense(192)),
+    layer(attention(8, 2, 64, 64, 0.11, 100, 10000.0, 32, (3.0, 1.0, 5.0, 128)), moe(8, 2, 64, 96)),
+    layer(latent(4, 32, 16, 32, 64, 0.14, 70, 80000.0), dense(192)),
     layer(wkv(2, 64, 16), moe(8, 1, 32, 64)),
     layer(wkv(4, 32, 12), None),
     layer(attention(4, 4, 32, 48, 0.18, 130, 300.0, 12), dense(40)),
-], cap=30.0, loop=(0, 2, 3))
+], cap=25.0, loop=(0, 2, 3))
 # the whole model is the loop, run twice; a loop that runs once changes nothing
 CASE_E = model(90, 72, 1e-5, [
     layer(latent(3, 8, 8, 8, 16, 0.25, 12, 100.0), moe(4, 2, 24, 24)),
