@@ -296,3 +296,27 @@ def test_the_whole_oracle_is_causal_loops_and_caps(tmp_path):
     config_once = dict(config, loop={"start": 0, "stop": 2, "times": 1})
     _, once = P.forward(config_once, weights, tokens[:20])
     assert torch.allclose(once[1], streams[1]) and embedded.shape == (20, 72)
+
+
+def test_the_command_line_writes_random_weights_and_plans_the_cache(tmp_path):
+    from safetensors import safe_open
+    from typer.testing import CliRunner
+
+    from turboserve_b200.cli import app
+
+    runner = CliRunner()
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(C.CASE_A))
+    out = tmp_path / "model"
+    result = runner.invoke(app, ["engine", "random-weights", "--config", str(config), "--out", str(out), "--seed", "7"])
+    assert result.exit_code == 0, result.stdout
+    written = json.loads((out / "config.json").read_text())
+    assert written["architecture"] == "Lorozen" and written["loop"] == C.CASE_A["loop"] and written["logit_softcap"] == 20.0
+    with safe_open(str(out / "model.safetensors"), "pt") as f:
+        names = set(f.keys())
+        assert {"embed", "head", "final.norm", "l0.mix.sink", "l0.mix.q.b", "l0.norm1b", "l2.mix.g", "l1.mix.w0", "l0.mlp.e5.down"} <= names
+        assert f.get_tensor("l0.mix.sink").dtype == torch.bfloat16
+    result = runner.invoke(app, ["engine", "kv-size", "-m", str(out), "--total-memory-gib", "1", "--block-size", "16",
+                                 "--max-num-seqs", "4", "--max-model-len", "256", "--dtype", "bfloat16"])
+    assert result.exit_code == 0, result.stdout
+    assert json.loads(result.stdout)["num_blocks"] >= 4

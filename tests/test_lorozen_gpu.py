@@ -634,3 +634,27 @@ def test_the_command_line_serves_a_folder(folders, tmp_path):
     assert done.returncode == 0 and "done 0" in done.stdout, done.stderr[-2000:]
     got = torch.frombuffer(bytearray((tmp_path / "out" / "0.f32").read_bytes()), dtype=torch.float32).reshape(2, config["vocab"])
     C.check(got, P.logits_of(config, weights, tokens)[[0, 5]], "float32", "trace_run")
+
+
+def test_generate_from_the_command_line_with_the_engines_sampler(folders):
+    """``engine generate`` on a folder of this design: greedy tokens are the plain ones, and sampling with a seed, a
+    temperature, top-p, a repetition penalty and log-probabilities runs through the same step."""
+    from typer.testing import CliRunner
+
+    from turboserve_b200.cli import app
+
+    runner = CliRunner()
+    folder = folders["E", False]
+    config, weights = P.read_model_folder(folder)
+    prompt = [5, 17, 3, 60, 2]
+    result = runner.invoke(app, ["engine", "generate", "-m", str(folder), "--prompt-ids", ",".join(map(str, prompt)), "--max-tokens", "6",
+                                 "--ignore-eos", "--num-blocks", "32", "--dtype", "float32", "--temperature", "0"])
+    assert result.exit_code == 0, result.stdout
+    line = next(line for line in result.stdout.splitlines() if line.startswith("output "))
+    assert json.loads(line.split(": ", 1)[1]) == P.greedy(config, weights, prompt, 6)
+    result = runner.invoke(app, ["engine", "generate", "-m", str(folder), "--prompt-ids", "5,17,3,5,17,3", "--max-tokens", "8", "--ignore-eos",
+                                 "--num-blocks", "32", "--temperature", "0.8", "--top-p", "0.9", "--seed", "3", "--repetition-penalty", "1.3",
+                                 "--logprobs"])
+    assert result.exit_code == 0, result.stdout
+    values = [float(v) for v in next(line for line in result.stdout.splitlines() if line.strip().startswith("logprobs:")).split(":", 1)[1].split()]
+    assert len(values) == 8 and all(v <= 0.0 for v in values)

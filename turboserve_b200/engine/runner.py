@@ -11,6 +11,7 @@ reference splits the same work over ``ModelRunner.execute``
 
 from __future__ import annotations
 
+import gc
 from pathlib import Path
 from typing import Sequence
 
@@ -246,13 +247,22 @@ class ModelRunner:
         torch.cuda.current_stream(self.device).wait_stream(stream)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            logits = self.run(static.batch)
-            if self.step_sampler is not None:
-                batch = static.batch  # row i holds the logits of token i, which is request i's (or padding)
-                self.step_sampler.sample_by_slot(logits, batch.state_slots, batch.seq_of_token, batch.context_lens,
-                                                 bucket, self.token_out, step_tokens=batch.token_ids,
-                                                 logprobs=self.logprob_out)
+        # Python's collector must not run inside the capture: the finalisers of what it frees (graphs and tensors of
+        # an engine that was dropped earlier) call the CUDA runtime, which ends the capture with an error
+        gc.collect()
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                logits = self.run(static.batch)
+                if self.step_sampler is not None:
+                    batch = static.batch  # row i holds the logits of token i, which is request i's (or padding)
+                    self.step_sampler.sample_by_slot(logits, batch.state_slots, batch.seq_of_token, batch.context_lens,
+                                                     bucket, self.token_out, step_tokens=batch.token_ids,
+                                                     logprobs=self.logprob_out)
+        finally:
+            if collecting:
+                gc.enable()
         entry = (graph, static, logits)
         self._graphs[(bucket, skew)] = entry
         self.num_graph_captures += 1
